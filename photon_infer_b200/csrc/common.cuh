@@ -1,0 +1,64 @@
+// Shared helpers of the sm_100a kernels: storage types, 32-bit conversion, block
+// reductions with a fixed order, the error word that kernels write on a bad index.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define PHOTON_API extern "C" __attribute__((visibility("default")))
+
+// dtype codes shared with kernels/ops.py
+#define PHOTON_F32 0
+#define PHOTON_BF16 1
+
+// launcher return codes below zero are argument errors found on the host
+#define PHOTON_ERR_UNSUPPORTED (-2)
+#define PHOTON_ERR_ARGUMENT (-3)
+
+// codes that kernels write into the error word (int32[4]: code, detail0, detail1, detail2)
+#define PHOTON_DEV_BAD_TOKEN 1
+#define PHOTON_DEV_BAD_SLOT 2
+#define PHOTON_DEV_BAD_PAGE 3
+#define PHOTON_DEV_WAIT_TIMEOUT 4
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// Loads a weight that may be stored in either type (norm weights keep 32-bit storage).
+__device__ __forceinline__ float load_w(const void* w, int is_bf16, size_t i) {
+  return is_bf16 ? __bfloat162float(((const bf16*)w)[i]) : ((const float*)w)[i];
+}
+
+__device__ __forceinline__ void report_error(int* err, int code, int d0, int d1, int d2) {
+  if (err != nullptr && atomicCAS(err, 0, code) == 0) { err[1] = d0; err[2] = d1; err[3] = d2; }
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over the block; every thread gets the result.  The order depends only on blockDim.
+__device__ __forceinline__ float block_sum(float v, float* smem32) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) smem32[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarp) ? smem32[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+static inline int launch_status() { return (int)cudaGetLastError(); }

@@ -1,0 +1,126 @@
+// Row-wise kernels of the decoder: embedding lookup, residual add fused with RMSNorm
+// (on all rows or on a list of rows), SwiGLU.  All arithmetic is 32-bit; storage is
+// float or bfloat16.  Formulas: include/photon/ops/kernels/rmsnorm_kernel.hpp:71-86
+// (w * (x * 1/sqrt(mean(x^2)+eps))), include/photon/ops/kernels/swiglu_kernel.hpp:67-76
+// (g / (1 + exp(-g)) * u), include/photon/ops/kernels/embedding_kernel.hpp:85-121.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+template <typename TW>
+__global__ void embedding_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
+                                 float* __restrict__ out, int H, int V, int* err) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* o = out + (size_t)t * H;
+  if (id < 0 || id >= V) {
+    if (threadIdx.x == 0) report_error(err, PHOTON_DEV_BAD_TOKEN, t, id, V);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = 0.f;
+    return;
+  }
+  const TW* row = table + (size_t)id * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]);
+}
+
+PHOTON_API int photon_embedding(const int* ids, const void* table, int table_dtype, float* out,
+                                int T, int H, int V, int* err, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const int threads = H >= 1024 ? 256 : 128;
+  if (table_dtype == PHOTON_BF16)
+    embedding_kernel<bf16><<<T, threads, 0, stream>>>(ids, (const bf16*)table, out, H, V, err);
+  else
+    embedding_kernel<float><<<T, threads, 0, stream>>>(ids, (const float*)table, out, H, V, err);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- add + RMSNorm
+// residual (float, in place) += delta; out = w * (residual * r).  rows == nullptr: row = blockIdx.x
+// of both residual and out.  rows != nullptr: reads row rows[blockIdx.x] and does NOT write the sum
+// back (the listed rows are only read; out has one row per list entry).
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_kernel(const TD* __restrict__ delta, float* __restrict__ residual,
+                                   const void* __restrict__ w, int w_bf16, TO* __restrict__ out,
+                                   const int* __restrict__ rows, int H, float eps) {
+  __shared__ float red[32];
+  extern __shared__ float stash[];               // H floats: the summed row
+  const int r = rows ? rows[blockIdx.x] : blockIdx.x;
+  float* res = residual + (size_t)r * H;
+  const TD* d = delta ? delta + (size_t)r * H : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = res[i];
+    if (d) v += to_f32(d[i]);
+    stash[i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+  TO* o = out + (size_t)blockIdx.x * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = stash[i];
+    if (d && !rows) res[i] = v;
+    o[i] = from_f32<TO>(load_w(w, w_bf16, i) * (v * inv));
+  }
+}
+
+template <typename TD, typename TO>
+static int add_rmsnorm_launch(const void* delta, float* residual, const void* w, int w_bf16, void* out,
+                              const int* rows, int n, int H, float eps, cudaStream_t stream) {
+  const size_t smem = (size_t)H * sizeof(float);
+  if (smem > 200 * 1024) return PHOTON_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  int threads = 128;
+  while (threads < 1024 && threads * 4 < H) threads <<= 1;   // depends on H only
+  add_rmsnorm_kernel<TD, TO><<<n, threads, smem, stream>>>((const TD*)delta, residual, w, w_bf16,
+                                                           (TO*)out, rows, H, eps);
+  return launch_status();
+}
+
+// delta may be null (plain norm).  delta_dtype / out_dtype: PHOTON_F32 or PHOTON_BF16.
+PHOTON_API int photon_add_rmsnorm(const void* delta, int delta_dtype, float* residual, const void* w,
+                                  int w_dtype, void* out, int out_dtype, const int* rows, int n, int H,
+                                  float eps, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int wb = (w_dtype == PHOTON_BF16);
+  if (delta_dtype == PHOTON_BF16 && out_dtype == PHOTON_BF16)
+    return add_rmsnorm_launch<bf16, bf16>(delta, residual, w, wb, out, rows, n, H, eps, stream);
+  if (delta_dtype == PHOTON_F32 && out_dtype == PHOTON_F32)
+    return add_rmsnorm_launch<float, float>(delta, residual, w, wb, out, rows, n, H, eps, stream);
+  if (delta_dtype == PHOTON_F32 && out_dtype == PHOTON_BF16)
+    return add_rmsnorm_launch<float, bf16>(delta, residual, w, wb, out, rows, n, H, eps, stream);
+  if (delta_dtype == PHOTON_BF16 && out_dtype == PHOTON_F32)
+    return add_rmsnorm_launch<bf16, float>(delta, residual, w, wb, out, rows, n, H, eps, stream);
+  return PHOTON_ERR_ARGUMENT;
+}
+
+// ---------------------------------------------------------------- SwiGLU
+// gate_up [T, 2*I]: columns [0, I) are the gate, [I, 2I) the up projection.  out [T, I].
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I, size_t total) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < total; idx += stride) {
+    const size_t t = idx / I;
+    const int i = (int)(idx - t * I);
+    const float g = to_f32(gate_up[t * 2 * I + i]);
+    const float u = to_f32(gate_up[t * 2 * I + I + i]);
+    const float s = g / (1.0f + expf(-g));
+    out[idx] = from_f32<T>(s * u);
+  }
+}
+
+PHOTON_API int photon_swiglu(const void* gate_up, void* out, int dtype, int T, int I, cudaStream_t stream) {
+  const size_t total = (size_t)T * I;
+  if (total == 0) return 0;
+  const int threads = 256;
+  size_t blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (dtype == PHOTON_BF16)
+    swiglu_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, total);
+  else
+    swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, total);
+  return launch_status();
+}

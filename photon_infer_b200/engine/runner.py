@@ -1,0 +1,170 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A step may hold portions of prompts beside single decoded tokens, cut anywhere.  It
+runs only the tokens it is given, as one batch, against the cache that earlier steps
+left, and returns 32-bit logits at the wanted places.  The reference's counterpart is
+``LLaMAModel::forward_batched`` (src/arch/llama_model.cpp:483-605), which rebuilds and
+uploads block tables in every layer (src/arch/transformer_block.cpp:455-465,496-509);
+here all indices of a step are built once on the host and reach the device in one copy.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..errors import ErrorCode, PhotonError
+from ..models.model import CausalLM
+from ..parts.base import GroupView, StepContext
+
+
+@dataclasses.dataclass
+class StepEntry:
+    request_id: object
+    tokens: Sequence[int]
+    want: Sequence[int] = ()            # indices into ``tokens`` whose logits are wanted
+
+
+@dataclasses.dataclass
+class StepResult:
+    logits: torch.Tensor                # float32 [n_wanted, vocab] on the device
+    rows: List[tuple]                   # (request_id, position in the request) of each row
+
+
+_DEVICE_ERRORS = {1: "token id {1} at token {0} of the step is outside the vocabulary of {2}",
+                  2: "token {0} of the step was given cache slot {1}, outside the pool of {2} slots",
+                  3: "token {0} of the step needs key {1}, whose block-table entry is {2}",
+                  4: "a kernel gave up waiting (stage {0}, {1}, {2})"}
+
+
+class ModelRunner:
+    def __init__(self, model: CausalLM, cache: CacheManager, max_model_len: Optional[int] = None):
+        self.model = model
+        self.cache = cache
+        self.device = model.device
+        self.max_model_len = max_model_len or model.spec.max_position
+        self.error_flag = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._layer_caches = cache.layer_caches()
+        self._pinned: Optional[torch.Tensor] = None
+        self._copy_done: Optional[torch.cuda.Event] = None
+        self.steps = 0
+        self.tokens = 0
+
+    # ------------------------------------------------------------------ host buffers
+    def _staging(self, n: int) -> torch.Tensor:
+        if self._pinned is None or self._pinned.numel() < n:
+            self._pinned = torch.empty(max(n, 1 << 14), dtype=torch.int32, pin_memory=True)
+        return self._pinned
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[StepEntry]) -> StepResult:
+        entries = [e for e in entries if len(e.tokens) > 0]
+        if not entries:
+            return StepResult(torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device), [])
+        cache = self.cache
+        seen = set()
+        for e in entries:
+            if e.request_id in seen:
+                raise PhotonError(ErrorCode.INVALID_ARGUMENT, f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            if not cache.has_request(e.request_id):
+                raise PhotonError(ErrorCode.INVALID_STATE, f"request {e.request_id!r} is not registered with the cache")
+            if cache.length(e.request_id) + len(e.tokens) > self.max_model_len:
+                raise PhotonError(ErrorCode.INVALID_ARGUMENT,
+                                  f"request {e.request_id!r} would exceed the longest request of {self.max_model_len} tokens")
+            for w in e.want:
+                if not 0 <= w < len(e.tokens):
+                    raise PhotonError(ErrorCode.INVALID_INDEX, f"wanted place {w} is outside the {len(e.tokens)} tokens given")
+        # pages first: all or nothing over the whole step
+        need = [0] * len(cache.groups)
+        for e in entries:
+            for g, n in enumerate(cache.pages_needed(e.request_id, len(e.tokens))):
+                need[g] += n
+        for g, n in enumerate(need):
+            if n > cache.groups[g].pool.num_free:
+                raise PhotonError(ErrorCode.OUT_OF_MEMORY,
+                                  f"the step needs {n} more cache pages in group {g}, "
+                                  f"{cache.groups[g].pool.num_free} of {cache.groups[g].num_pages} are free")
+        for e in entries:
+            cache.extend(e.request_id, len(e.tokens))
+
+        ctx, logit_rows, rows = self._build_context(entries)
+        logits = self.model.forward(ctx, self._layer_caches, logit_rows)
+        for e in entries:
+            cache.commit(e.request_id, len(e.tokens))
+        self.steps += 1
+        self.tokens += ctx.num_tokens
+        return StepResult(logits, rows)
+
+    def _build_context(self, entries: Sequence[StepEntry]):
+        cache = self.cache
+        S = len(entries)
+        q_lens = [len(e.tokens) for e in entries]
+        starts = [cache.length(e.request_id) for e in entries]
+        T = sum(q_lens)
+        rids = [e.request_id for e in entries]
+        n_want = sum(len(e.want) for e in entries)
+        widths = cache.table_width(rids)
+        G = len(cache.groups)
+        # layout of the one staging buffer (int32 counts)
+        sizes = [T, T, T, S + 1, S, S, n_want] + [T] * G + [S * w for w in widths]
+        offs = np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])]).astype(np.int64)
+        total = int(offs[-1])
+        if self._copy_done is not None:
+            self._copy_done.synchronize()
+        stage = self._staging(total)
+        host = stage.numpy()
+        seg = lambda i: host[offs[i]: offs[i] + sizes[i]]
+        tok, pos, tseq, cu, ctxl, slots, lrows = (seg(i) for i in range(7))
+        t = 0
+        rows: List[tuple] = []
+        w = 0
+        for s, e in enumerate(entries):
+            n = q_lens[s]
+            tok[t:t + n] = np.asarray(e.tokens, dtype=np.int64)
+            pos[t:t + n] = np.arange(starts[s], starts[s] + n)
+            tseq[t:t + n] = s
+            cu[s] = t
+            ctxl[s] = starts[s] + n
+            slots[s] = cache.states.slot_of(e.request_id)
+            for k in e.want:
+                lrows[w] = t + k
+                rows.append((e.request_id, starts[s] + k))
+                w += 1
+            t += n
+        cu[S] = T
+        for g in range(G):
+            sm = seg(7 + g)
+            t = 0
+            for s, e in enumerate(entries):
+                cache.fill_slot_mapping(g, e.request_id, starts[s], q_lens[s], sm[t:t + q_lens[s]])
+                t += q_lens[s]
+            cache.fill_block_table(g, rids, seg(7 + G + g).reshape(S, widths[g]))
+        dev = stage[:total].to(self.device, non_blocking=True)
+        dseg = lambda i: dev[offs[i]: offs[i] + sizes[i]]
+        groups = [GroupView(block_table=dseg(7 + G + g).view(S, widths[g]), slot_mapping=dseg(7 + g),
+                            page_size=cache.groups[g].page_size, num_pages=cache.groups[g].num_pages,
+                            max_pages_per_seq=widths[g]) for g in range(G)]
+        ctx = StepContext(
+            num_tokens=T, num_seqs=S, dtype=self.model.dtype,
+            token_ids=dseg(0), positions=dseg(1), token_seq=dseg(2), cu_tokens=dseg(3),
+            context_lens=dseg(4), state_slots=dseg(5), groups=groups,
+            host_query_lens=q_lens, host_context_lens=[a + b for a, b in zip(starts, q_lens)],
+            host_start_positions=starts, max_query_len=max(q_lens),
+            max_context_len=max(a + b for a, b in zip(starts, q_lens)), error_flag=self.error_flag)
+        # the staging buffer is reused by the next step, which waits for this copy first
+        self._copy_done = torch.cuda.Event()
+        self._copy_done.record()
+        return ctx, dseg(6), rows
+
+    # ------------------------------------------------------------------ errors from the device
+    def check_device_errors(self) -> None:
+        """Reads the error word the kernels write (a device-to-host copy and a wait)."""
+        flag = self.error_flag.cpu().tolist()
+        if flag[0] != 0:
+            self.error_flag.zero_()
+            msg = _DEVICE_ERRORS.get(flag[0], "device error code {0}").format(flag[1], flag[2], flag[3])
+            raise PhotonError(ErrorCode.INVALID_INDEX, msg)

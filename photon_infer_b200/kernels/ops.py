@@ -1,0 +1,267 @@
+"""Python side of the CUDA kernels: argument checks, pointers, the current stream.
+
+Every function takes CUDA tensors and launches on ``torch.cuda.current_stream()``.
+There is no CPU path: a tensor that is not on a CUDA device raises, and so does a
+missing or failing extension (``csrc/build.py``).  A kernel that cannot run a size
+correctly refuses it (``UNSUPPORTED_SIZE``) instead of giving a wrong result.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_long, c_void_p
+from typing import Optional
+
+import torch
+
+from ..csrc.build import load_module
+from ..errors import ErrorCode, PhotonError
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+_launch_count = 0
+
+
+def launch_count() -> int:
+    """Kernels of this package launched so far in this process."""
+    return _launch_count
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, f"dtype {t.dtype} is not supported (float32 or bfloat16)") from None
+
+
+def _cuda(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise PhotonError(ErrorCode.INVALID_ARGUMENT,
+                              "a tensor on the CPU was passed to a CUDA kernel; there is no CPU path")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(t.data_ptr() if t is not None else 0)
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(status: int, what: str) -> None:
+    global _launch_count
+    if status == 0:
+        _launch_count += 1
+        return
+    if status == -2:
+        raise PhotonError(ErrorCode.UNSUPPORTED_SIZE, f"{what}: this size is not supported by the kernel")
+    if status == -3:
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, f"{what}: invalid argument")
+    raise PhotonError(ErrorCode.CUDA_ERROR, f"{what}: CUDA error {status}")
+
+
+_sigs_done = set()
+
+
+def _fn(module: str, name: str, argtypes, defines=None):
+    lib = load_module(module, defines)
+    f = getattr(lib, name)
+    key = (id(lib), name)
+    if key not in _sigs_done:
+        f.argtypes = argtypes
+        f.restype = c_int
+        _sigs_done.add(key)
+    return f
+
+
+def _int32(t: torch.Tensor, what: str) -> None:
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, f"{what} must be a contiguous int32 tensor")
+
+
+# ----------------------------------------------------------------------------- row kernels
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: Optional[torch.Tensor]) -> None:
+    """``out[t, :] = table[ids[t], :]`` as float32; ids outside the table set the error word."""
+    _cuda(ids, table, out, err)
+    _int32(ids, "ids")
+    T, (V, H) = ids.numel(), table.shape
+    if out.dtype != torch.float32 or out.shape != (T, H) or not out.is_contiguous() or not table.is_contiguous():
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "embedding: out must be contiguous float32 [T, H]")
+    f = _fn("elementwise", "photon_embedding",
+            [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(ids), _ptr(table), _dtype_code(table), _ptr(out), T, H, V, _ptr(err), _stream()), "embedding")
+
+
+def add_rmsnorm(delta: Optional[torch.Tensor], residual: torch.Tensor, weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """``residual += delta`` in float32 (in place; skipped when ``rows`` is given), then
+    ``out = weight * (residual / sqrt(mean(residual^2) + eps))``.  With ``rows`` (int32 list)
+    only those rows are read and ``out`` has one row per list entry."""
+    _cuda(delta, residual, weight, out, rows)
+    H = residual.shape[-1]
+    n = rows.numel() if rows is not None else residual.shape[0]
+    if residual.dtype != torch.float32 or not residual.is_contiguous():
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "add_rmsnorm: the residual stream must be contiguous float32")
+    if delta is not None and (delta.shape != residual.shape or not delta.is_contiguous()):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "add_rmsnorm: delta must match the residual stream")
+    if out.shape != (n, H) or not out.is_contiguous() or weight.numel() != H:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "add_rmsnorm: out must be [rows, H] and weight [H]")
+    if rows is not None:
+        _int32(rows, "rows")
+    f = _fn("elementwise", "photon_add_rmsnorm",
+            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p])
+    _check(f(_ptr(delta), _dtype_code(delta) if delta is not None else F32, _ptr(residual), _ptr(weight),
+             _dtype_code(weight), _ptr(out), _dtype_code(out), _ptr(rows), n, H, float(eps), _stream()),
+           "add_rmsnorm")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """``out = silu(gate_up[:, :I]) * gate_up[:, I:]``."""
+    _cuda(gate_up, out)
+    T, I2 = gate_up.shape
+    if I2 % 2 or out.shape != (T, I2 // 2) or out.dtype != gate_up.dtype \
+            or not gate_up.is_contiguous() or not out.is_contiguous():
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "swiglu: gate_up [T, 2I] and out [T, I] of one dtype")
+    f = _fn("elementwise", "photon_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(gate_up), _ptr(out), _dtype_code(out), T, I2 // 2, _stream()), "swiglu")
+
+
+# ----------------------------------------------------------------------------- rope and cache write
+
+def rope_kv_write(q: Optional[torch.Tensor], k: Optional[torch.Tensor], v: Optional[torch.Tensor],
+                  positions: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], interleaved: bool,
+                  slot_mapping: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                  v_cache: Optional[torch.Tensor], n_q: int, n_kv: int, head_dim: int,
+                  err: Optional[torch.Tensor]) -> None:
+    """Rotates ``q [T, n_q * d]`` and ``k [T, n_kv * d]`` in place (when ``inv_freq`` is given)
+    and stores ``k`` and ``v [T, n_kv * d]`` at ``slot_mapping`` in the paged cache
+    ``[pages, n_kv, page_size, d]`` (when the caches are given).  The three inputs may be
+    views with any row stride, e.g. sections of one fused row."""
+    _cuda(q, k, v, positions, inv_freq, slot_mapping, k_cache, v_cache, err)
+    ref = q if q is not None else k
+    if ref is None:
+        return
+    T = ref.shape[0]
+    for name, t, heads in (("q", q, n_q), ("k", k, n_kv), ("v", v, n_kv)):
+        if t is None:
+            continue
+        if t.dim() == 3:
+            ok = t.shape == (T, heads, head_dim) and t.stride(2) == 1 and t.stride(1) == head_dim
+        else:
+            ok = t.shape == (T, heads * head_dim) and t.stride(1) == 1
+        if not ok or t.dtype != ref.dtype:
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH,
+                              f"rope_kv_write: {name} must be [T, {heads} * {head_dim}] with contiguous heads")
+    rotate = inv_freq is not None
+    write = k_cache is not None
+    page_size, num_slots = 1, 0
+    if rotate:
+        _int32(positions, "positions")
+        if inv_freq.dtype != torch.float32 or inv_freq.numel() != head_dim // 2 or head_dim % 2:
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, "rope_kv_write: inv_freq must be float32 [head_dim / 2]")
+    if write:
+        if k is None or v is None:
+            raise PhotonError(ErrorCode.INVALID_ARGUMENT, "rope_kv_write: storing needs k and v")
+        _int32(slot_mapping, "slot_mapping")
+        if k_cache.dtype != ref.dtype or v_cache.dtype != ref.dtype or k_cache.shape != v_cache.shape \
+                or k_cache.dim() != 4 or k_cache.shape[1] != n_kv or k_cache.shape[3] != head_dim \
+                or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH,
+                              "rope_kv_write: caches must be contiguous [pages, n_kv, page_size, head_dim] of the run dtype")
+        page_size = k_cache.shape[2]
+        num_slots = k_cache.shape[0] * page_size
+    f = _fn("rope_kv", "photon_rope_kv_write",
+            [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_void_p, c_int, c_void_p,
+             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_long, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(q), q.stride(0) if q is not None else 0, _ptr(k), k.stride(0) if k is not None else 0,
+             _ptr(v), v.stride(0) if v is not None else 0, _dtype_code(ref), _ptr(positions), _ptr(inv_freq),
+             int(interleaved), _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), T, n_q, n_kv, head_dim,
+             page_size, num_slots, int(rotate), int(write), _ptr(err), _stream()), "rope_kv_write")
+
+
+# ----------------------------------------------------------------------------- attention
+
+def paged_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    block_table: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
+                    n_q: int, n_kv: int, head_dim: int, window: Optional[int], scale: float,
+                    err: Optional[torch.Tensor]) -> None:
+    """General paged causal attention.  ``q`` is a ``[T, n_q * d]`` view (row stride free),
+    ``out [T, n_q * d]``; the token at position ``p`` of request ``token_seq[t]`` sees keys
+    ``max(0, p - window + 1) .. p`` through ``block_table[seq]``."""
+    _cuda(q, out, k_cache, v_cache, block_table, token_seq, positions, err)
+    T = q.shape[0]
+    if q.shape[1] != n_q * head_dim or q.stride(1) != 1 or out.shape != (T, n_q * head_dim) or out.stride(1) != 1:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "paged_attention: q and out must be [T, n_q * head_dim]")
+    if q.dtype != out.dtype or q.dtype != k_cache.dtype or q.dtype != v_cache.dtype:
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "paged_attention: q, out and the caches must share one dtype")
+    if n_kv <= 0 or n_q % n_kv or head_dim % 2:
+        raise PhotonError(ErrorCode.UNSUPPORTED_SIZE, "paged_attention: n_q must be a multiple of n_kv and head_dim even")
+    if (n_q // n_kv) * head_dim > 4096:
+        raise PhotonError(ErrorCode.UNSUPPORTED_SIZE,
+                          f"paged_attention: heads per group x head_dim = {(n_q // n_kv) * head_dim} exceeds 4096")
+    for name, t in (("block_table", block_table), ("token_seq", token_seq), ("positions", positions)):
+        _int32(t, name)
+    f = _fn("attention", "photon_paged_attention",
+            [c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _dtype_code(q), _ptr(k_cache), _ptr(v_cache),
+             _ptr(block_table), block_table.shape[1], _ptr(token_seq), _ptr(positions), T, n_q, n_kv, head_dim,
+             k_cache.shape[2], k_cache.shape[0], int(window) if window else 0, float(scale), _ptr(err), _stream()),
+           "paged_attention")
+
+
+# ----------------------------------------------------------------------------- matrix products
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``x [M, K] @ weight[N, K]^T``.  float32: this package's FMA kernel (true 32-bit).
+    bfloat16: the library product (cuBLAS through torch), where the reference's engine
+    also calls the library (src/ops/kernels/cuda/matmul_dequant_cached.cu:193-207)."""
+    _cuda(x, weight, out)
+    M, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K or x.stride(1) != 1 or not weight.is_contiguous():
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, f"linear: x [M, {K}] against weight {tuple(weight.shape)}")
+    if x.dtype != weight.dtype:
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, f"linear: x is {x.dtype}, weight is {weight.dtype}")
+    want = out_dtype or x.dtype
+    if x.dtype == torch.float32:
+        if want != torch.float32:
+            raise PhotonError(ErrorCode.INVALID_ARGUMENT, "linear: a float32 product gives float32")
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+        f = _fn("gemm_f32", "photon_sgemm_nt",
+                [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_void_p])
+        _check(f(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K, _stream()),
+               "sgemm")
+        return out
+    if want == torch.float32:
+        res = torch.mm(x, weight.t(), out_dtype=torch.float32)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+    if out is None:
+        return torch.mm(x, weight.t())
+    torch.mm(x, weight.t(), out=out)
+    return out
+
+
+# ----------------------------------------------------------------------------- sampling
+
+def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], u: Optional[torch.Tensor],
+           out: torch.Tensor) -> None:
+    """Row-wise: first-maximum argmax where ``temperature <= 0`` (or None), else the first
+    index whose running sum of ``softmax(logits / temperature)`` reaches ``u``."""
+    _cuda(logits, temperature, u, out)
+    rows, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "sample: logits must be float32 with unit inner stride")
+    _int32(out, "out")
+    if temperature is not None and (temperature.dtype != torch.float32 or temperature.numel() != rows
+                                    or u is None or u.dtype != torch.float32 or u.numel() != rows):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "sample: temperature and u must be float32 [rows]")
+    f = _fn("sampling", "photon_sample", [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(logits), logits.stride(0), _ptr(temperature), _ptr(u), _ptr(out), rows, V, _stream()), "sample")

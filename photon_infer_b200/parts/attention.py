@@ -1,0 +1,99 @@
+"""Grouped-query attention over the paged cache.
+
+Order of work as src/arch/transformer_block.cpp:204-266: q, k, v projections (one
+fused product here), rotation of q and k, keys and values into the cache, attention
+of every token over the keys up to its own position, output projection.  The
+reference's batched path rotates every row with the first token's position and lets
+a token see later tokens of its own portion (src/arch/transformer_block.cpp:442-445,
+486-509); here each token has its own position and its own causal limit.
+
+``window`` None is full attention; an integer makes the same mixer a sliding-window
+one, whose cache group gives pages back once the window has passed them.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+
+from ..kernels import ops
+from .base import LayerCache, Mixer, PagedCacheSpec, StepContext, TensorSpec
+from .linear import project
+from .registry import register_mixer
+from .rope import RotaryEncoding
+
+
+class PagedAttention(Mixer):
+    kernel_modules = ("rope_kv", "attention", "gemm_f32")
+
+    def __init__(self, hidden_size: int, n_q_heads: int, n_kv_heads: int, head_dim: int,
+                 position_encoding=None, window: Optional[int] = None, scale: Optional[float] = None):
+        self.hidden_size = hidden_size
+        self.n_q = n_q_heads
+        self.n_kv = n_kv_heads
+        self.head_dim = head_dim
+        self.window = window
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.position_encoding = position_encoding
+        self.w_qkv: Optional[torch.Tensor] = None
+        self.w_o: Optional[torch.Tensor] = None
+
+    # -- weights: separate q/k/v in the file, one fused matrix on the device
+    def tensor_specs(self) -> List[TensorSpec]:
+        d, H = self.head_dim, self.hidden_size
+        return [TensorSpec("q_proj.weight", (self.n_q * d, H)),
+                TensorSpec("k_proj.weight", (self.n_kv * d, H)),
+                TensorSpec("v_proj.weight", (self.n_kv * d, H)),
+                TensorSpec("o_proj.weight", (H, self.n_q * d))]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.w_qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"],
+                                tensors["v_proj.weight"]], dim=0).contiguous()
+        self.w_o = tensors["o_proj.weight"].contiguous()
+
+    def weight_bytes(self) -> int:
+        return (self.w_qkv.numel() + self.w_o.numel()) * self.w_qkv.element_size()
+
+    def cache_spec(self) -> Optional[PagedCacheSpec]:
+        return PagedCacheSpec(self.n_kv, self.head_dim, self.window)
+
+    # -- one step
+    def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        T = h.shape[0]
+        d = self.head_dim
+        group = ctx.groups[cache.group]
+        if cache.shared:
+            # keys and values come from another entry's pages: only the queries are computed
+            q = project(h, self.w_qkv[: self.n_q * d])
+            k = v = None
+        else:
+            qkv = project(h, self.w_qkv)                              # [T, (n_q + 2 n_kv) d]
+            q = qkv[:, : self.n_q * d]
+            k = qkv[:, self.n_q * d: (self.n_q + self.n_kv) * d]
+            v = qkv[:, (self.n_q + self.n_kv) * d:]
+        pe = self.position_encoding
+        k_cache, v_cache = (None, None) if cache.shared else (cache.k, cache.v)
+        if isinstance(pe, RotaryEncoding):
+            # rotation and cache write in one pass over the row
+            ops.rope_kv_write(q, k, v, ctx.positions,
+                              pe.inv_freq, pe.interleaved, group.slot_mapping, k_cache, v_cache,
+                              self.n_q, self.n_kv, d, ctx.error_flag)
+        else:
+            if pe is not None:
+                pe.apply(q.view(T, self.n_q, d), None if k is None else k.view(T, self.n_kv, d), ctx.positions)
+            if k_cache is not None:
+                ops.rope_kv_write(None, k, v, None, None, False, group.slot_mapping, k_cache, v_cache,
+                                  self.n_q, self.n_kv, d, ctx.error_flag)
+        attn = torch.empty((T, self.n_q * d), dtype=h.dtype, device=h.device)
+        self.attend(q, attn, ctx, cache)
+        return project(attn, self.w_o)
+
+    def attend(self, q: torch.Tensor, out: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
+        group = ctx.groups[cache.group]
+        ops.paged_attention(q, out, cache.k, cache.v, group.block_table, ctx.token_seq, ctx.positions,
+                            self.n_q, self.n_kv, self.head_dim, self.window, self.scale, ctx.error_flag)
+
+
+register_mixer("full_attention", PagedAttention)
+register_mixer("sliding_attention", PagedAttention)

@@ -1,0 +1,347 @@
+"""Each CUDA kernel alone against a plain float32/float64 reference of the same op, at
+sizes other than the engine's tests use."""
+import math
+
+import pytest
+import torch
+
+from plain.llama_plain import (causal_attention, inverse_cdf_sample, rms_norm, rope_apply,
+                               rope_inverse_frequencies, swiglu, temperature_probabilities)
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def _tol(dtype):
+    # float32: summation order only.  bfloat16: one rounding of the output (2^-9 relative) plus
+    # the same on inputs that the reference reads after rounding, so nothing else.
+    return 2e-6 if dtype == torch.float32 else 6e-3
+
+
+def _close(got, want, dtype, scale=None):
+    want = want.double().cpu()
+    got = got.double().cpu()
+    s = float(want.abs().max()) if scale is None else scale
+    assert float((got - want).abs().max()) <= _tol(dtype) * max(s, 1e-30), \
+        f"max diff {float((got - want).abs().max()):.3g} at scale {s:.3g}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H,V", [(1, 24, 7), (13, 200, 101), (5, 2050, 33)])
+def test_embedding(dtype, T, H, V):
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(0)
+    table = torch.randn(V, H).to(dtype).to(DEV)
+    ids = torch.randint(0, V, (T,), dtype=torch.int32, device=DEV)
+    out = torch.empty(T, H, dtype=torch.float32, device=DEV)
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    ops.embedding(ids, table, out, err)
+    assert torch.equal(out.cpu(), table.float().cpu()[ids.cpu().long()])
+    assert err.cpu().tolist()[0] == 0
+
+
+def test_embedding_reports_bad_token():
+    from photon_infer_b200.kernels import ops
+    table = torch.randn(10, 8, device=DEV)
+    ids = torch.tensor([1, 12, 3], dtype=torch.int32, device=DEV)
+    out = torch.empty(3, 8, device=DEV)
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    ops.embedding(ids, table, out, err)
+    assert err.cpu().tolist() == [1, 1, 12, 10]
+    assert float(out[1].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H", [(1, 16), (7, 200), (3, 2048), (2, 5000), (2, 14000)])
+@pytest.mark.parametrize("w_dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(dtype, T, H, w_dtype):
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(1)
+    res = torch.randn(T, H)
+    delta = torch.randn(T, H).to(dtype)
+    w = (1 + 0.1 * torch.randn(H)).to(w_dtype)
+    eps = 3e-6
+    want_res = res + delta.float()
+    want = rms_norm(want_res.double(), w.double(), eps)
+    r = res.to(DEV).clone()
+    out = torch.empty(T, H, dtype=dtype, device=DEV)
+    ops.add_rmsnorm(delta.to(DEV), r, w.to(DEV), eps, out)
+    assert torch.equal(r.cpu(), want_res)
+    _close(out, want, dtype)
+    # without a delta, and on listed rows only
+    rows = torch.tensor([T - 1, 0], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(2, H, dtype=dtype, device=DEV)
+    r2 = res.to(DEV).clone()
+    ops.add_rmsnorm(delta.to(DEV), r2, w.to(DEV), eps, out2, rows=rows)
+    assert torch.equal(r2.cpu(), res)                       # listed rows are only read
+    _close(out2, want[[T - 1, 0]], dtype)
+    out3 = torch.empty(T, H, dtype=dtype, device=DEV)
+    ops.add_rmsnorm(None, r2, w.to(DEV), eps, out3)
+    _close(out3, rms_norm(res.double(), w.double(), eps), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,I", [(1, 8), (9, 200), (300, 1111)])
+def test_swiglu(dtype, T, I):
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(2)
+    gu = (3 * torch.randn(T, 2 * I)).to(dtype)
+    out = torch.empty(T, I, dtype=dtype, device=DEV)
+    ops.swiglu(gu.to(DEV), out)
+    _close(out, swiglu(gu[:, :I].double(), gu[:, I:].double()), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("n_q,n_kv,d,ps", [(4, 2, 16, 16), (3, 1, 32, 8), (6, 2, 48, 16), (2, 2, 128, 4), (5, 5, 80, 32)])
+def test_rope_and_cache_write(dtype, interleaved, n_q, n_kv, d, ps):
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(3)
+    T, pages = 11, 9
+    qkv = torch.randn(T, (n_q + 2 * n_kv) * d).to(dtype)
+    positions = torch.tensor([0, 1, 2, 3, 77, 500, 4095, 9, 10, 70000, 12], dtype=torch.int32)
+    scaling = dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                   original_max_position_embeddings=64)
+    inv = rope_inverse_frequencies(d, 500000.0, scaling)
+    slots = torch.randperm(pages * ps)[:T].to(torch.int32)
+    kc = torch.zeros(pages, n_kv, ps, d, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    buf = qkv.to(DEV).clone()
+    q = buf[:, : n_q * d]
+    k = buf[:, n_q * d: (n_q + n_kv) * d]
+    v = buf[:, (n_q + n_kv) * d:]
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    ops.rope_kv_write(q, k, v, positions.to(DEV), inv.to(DEV), interleaved, slots.to(DEV), kc, vc, n_q, n_kv, d, err)
+    assert err.cpu().tolist()[0] == 0
+    src = qkv.double()
+    want_q = rope_apply(src[:, : n_q * d].view(T, n_q, d), positions, inv, interleaved)
+    want_k = rope_apply(src[:, n_q * d: (n_q + n_kv) * d].view(T, n_kv, d), positions, inv, interleaved)
+    # the angle is a float32 product of a large position: allow its rounding (|x| * 2^-24 * pos ~ 1e-3 at 70000)
+    big = 4e-3 if dtype == torch.float32 else None
+    if dtype == torch.float32:
+        small = positions < 5000
+        _close(q.view(T, n_q, d)[small], want_q[small], dtype, scale=float(want_q.abs().max()) * 20)
+        assert float((q.view(T, n_q, d).cpu().double() - want_q).abs().max()) < big * float(want_q.abs().max())
+    else:
+        _close(q.view(T, n_q, d), want_q, dtype)
+    got_k = torch.stack([kc.cpu()[int(s) // ps, :, int(s) % ps, :] for s in slots])
+    got_v = torch.stack([vc.cpu()[int(s) // ps, :, int(s) % ps, :] for s in slots])
+    assert torch.equal(got_v, qkv[:, (n_q + n_kv) * d:].view(T, n_kv, d))
+    assert torch.equal(got_k, k.view(T, n_kv, d).cpu())
+    if dtype == torch.bfloat16:
+        _close(got_k, want_k, dtype)
+    # slots that were not named stay untouched
+    untouched = torch.ones(pages * ps, dtype=torch.bool)
+    untouched[slots.long()] = False
+    assert float(kc.cpu().permute(0, 2, 1, 3).reshape(pages * ps, -1)[untouched].abs().max()) == 0.0
+
+
+def test_rope_float32_matches_plain_exactly_enough():
+    """Same 32-bit angle as the plain implementation: agreement to float32 rounding at small positions."""
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(4)
+    T, n_q, n_kv, d = 64, 2, 1, 64
+    positions = torch.arange(T, dtype=torch.int32)
+    inv = rope_inverse_frequencies(d, 10000.0, None)
+    x = torch.randn(T, (n_q + 2 * n_kv) * d)
+    buf = x.to(DEV).clone()
+    ops.rope_kv_write(buf[:, : n_q * d], buf[:, n_q * d:(n_q + n_kv) * d], None, positions.to(DEV), inv.to(DEV),
+                      False, None, None, None, n_q, n_kv, d, None)
+    want = rope_apply(x[:, : n_q * d].view(T, n_q, d), positions, inv, False)
+    assert float((buf[:, : n_q * d].view(T, n_q, d).cpu() - want).abs().max()) < 2e-6 * float(want.abs().max())
+
+
+def _paged(k, v, ps, pages, seed):
+    """Scatter dense [L, n_kv, d] keys/values into a paged cache with a shuffled block table."""
+    L, n_kv, d = k.shape
+    n_logical = (L + ps - 1) // ps
+    g = torch.Generator().manual_seed(seed)
+    table = torch.randperm(pages, generator=g)[:n_logical]
+    kc = torch.full((pages, n_kv, ps, d), float("nan"), dtype=k.dtype)     # unwritten slots must never be read
+    vc = torch.full((pages, n_kv, ps, d), float("nan"), dtype=k.dtype)
+    for t in range(L):
+        kc[table[t // ps], :, t % ps] = k[t]
+        vc[table[t // ps], :, t % ps] = v[t]
+    return kc, vc, table
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q,n_kv,d,ps,window", [
+    (4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 2, 48, 16, 24), (8, 1, 64, 4, None), (2, 2, 128, 32, 70),
+    (5, 5, 80, 16, None), (16, 2, 256, 16, None), (7, 7, 16, 8, 5)])
+def test_paged_attention_two_requests(dtype, n_q, n_kv, d, ps, window):
+    """Two requests in one batch: a portion in the middle of one, a single late token of the other."""
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(5)
+    lens = [150, 97]
+    pages = 40
+    qs, ks, vs, outs = [], [], [], []
+    kc = vc = None
+    tables = []
+    for i, L in enumerate(lens):
+        q = torch.randn(L, n_q, d).to(dtype)
+        k = torch.randn(L, n_kv, d).to(dtype)
+        v = torch.randn(L, n_kv, d).to(dtype)
+        outs.append(causal_attention(q.double(), k.double(), v.double(), window=window))
+        qs.append(q); ks.append(k); vs.append(v)
+    # one shared pool: request 0 takes even pages, request 1 odd ones, shuffled
+    kc = torch.full((pages, n_kv, ps, d), float("nan"), dtype=dtype)
+    vc = torch.full_like(kc, float("nan"))
+    perm = torch.randperm(pages, generator=torch.Generator().manual_seed(9)).tolist()
+    width = max((L + ps - 1) // ps for L in lens) + 3
+    table = torch.full((2, width), -1, dtype=torch.int32)
+    for i, L in enumerate(lens):
+        for lp in range((L + ps - 1) // ps):
+            table[i, lp] = perm.pop()
+        for t in range(L):
+            kc[table[i, t // ps], :, t % ps] = ks[i][t]
+            vc[table[i, t // ps], :, t % ps] = vs[i][t]
+    # request 0: tokens 60..99 ; request 1: its last token
+    tok_seq = torch.tensor([0] * 40 + [1], dtype=torch.int32)
+    positions = torch.tensor(list(range(60, 100)) + [lens[1] - 1], dtype=torch.int32)
+    q = torch.cat([qs[0][60:100], qs[1][-1:]]).reshape(41, n_q * d)
+    want = torch.cat([outs[0][60:100], outs[1][-1:]]).reshape(41, n_q * d)
+    out = torch.empty(41, n_q * d, dtype=dtype, device=DEV)
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    ops.paged_attention(q.to(DEV), out, kc.to(DEV), vc.to(DEV), table.to(DEV), tok_seq.to(DEV), positions.to(DEV),
+                        n_q, n_kv, d, window, 1.0 / math.sqrt(d), err)
+    assert err.cpu().tolist()[0] == 0
+    assert not torch.isnan(out).any()
+    _close(out, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_far_key_stands_out(dtype):
+    """One key among hundreds is made to dominate: the output must be that key's value."""
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(6)
+    n_q, n_kv, d, ps, L = 4, 1, 64, 16, 700
+    for far in (0, 15, 16, 333, 511, 512, 699):
+        q = 0.1 * torch.randn(1, n_q, d)
+        k = 0.1 * torch.randn(L, n_kv, d)
+        v = torch.randn(L, n_kv, d)
+        k[far] = 0
+        k[far, 0, 0] = 40.0
+        q[0, :, 0] = 40.0                                    # score 1600/8 = 200 against O(1) elsewhere
+        kc, vc, table = _paged(k.to(dtype), v.to(dtype), ps, 50, seed=far)
+        out = torch.empty(1, n_q * d, dtype=dtype, device=DEV)
+        ops.paged_attention(q.to(dtype).reshape(1, -1).to(DEV), out, kc.to(DEV), vc.to(DEV),
+                            table.to(torch.int32).reshape(1, -1).to(DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+                            torch.tensor([L - 1], dtype=torch.int32, device=DEV), n_q, n_kv, d, None,
+                            1.0 / math.sqrt(d), None)
+        want = v[far, 0].to(dtype).float().repeat(n_q)
+        assert float((out.float().cpu()[0] - want).abs().max()) < 1e-3, f"far key {far}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_window_edge(dtype):
+    """The key just outside the window dominates in score but must be invisible."""
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(7)
+    n_q, n_kv, d, ps, L, window = 2, 1, 32, 8, 100, 24
+    q = 0.1 * torch.randn(1, n_q, d)
+    k = 0.1 * torch.randn(L, n_kv, d)
+    v = torch.randn(L, n_kv, d)
+    outside = L - 1 - window                                  # first invisible key
+    k[outside] = 0; k[outside, 0, 0] = 50.0
+    q[0, :, 0] = 50.0
+    kc, vc, table = _paged(k.to(dtype), v.to(dtype), ps, 20, seed=1)
+    args = (kc.to(DEV), vc.to(DEV), table.to(torch.int32).reshape(1, -1).to(DEV),
+            torch.zeros(1, dtype=torch.int32, device=DEV), torch.tensor([L - 1], dtype=torch.int32, device=DEV))
+    out = torch.empty(1, n_q * d, dtype=dtype, device=DEV)
+    ops.paged_attention(q.to(dtype).reshape(1, -1).to(DEV), out, *args, n_q, n_kv, d, window, 1.0 / math.sqrt(d), None)
+    want = causal_attention(q.to(dtype).double().expand(L, n_q, d).clone(), k.to(dtype).double(), v.to(dtype).double(),
+                            window=window)[-1].reshape(-1)
+    _close(out[0], want, dtype)
+    # with a window one larger the key is visible and takes over
+    ops.paged_attention(q.to(dtype).reshape(1, -1).to(DEV), out, *args, n_q, n_kv, d, window + 1, 1.0 / math.sqrt(d), None)
+    assert float((out.float().cpu()[0] - v[outside, 0].to(dtype).float().repeat(n_q)).abs().max()) < 1e-3
+
+
+def test_paged_attention_reports_missing_page():
+    from photon_infer_b200.kernels import ops
+    n_q, n_kv, d, ps = 2, 1, 16, 8
+    kc = torch.zeros(4, n_kv, ps, d, device=DEV)
+    table = torch.tensor([[0, -1, 2, -1]], dtype=torch.int32, device=DEV)
+    out = torch.empty(1, n_q * d, device=DEV)
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    ops.paged_attention(torch.zeros(1, n_q * d, device=DEV), out, kc, kc, table, torch.zeros(1, dtype=torch.int32, device=DEV),
+                        torch.tensor([20], dtype=torch.int32, device=DEV), n_q, n_kv, d, None, 0.25, err)
+    assert err.cpu().tolist()[0] == 3
+
+
+def test_paged_attention_refuses_oversized_group():
+    from photon_infer_b200.errors import PhotonError
+    from photon_infer_b200.kernels import ops
+    z = torch.zeros(1, 64 * 128, device=DEV)
+    kc = torch.zeros(1, 1, 8, 128, device=DEV)
+    i = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(PhotonError):
+        ops.paged_attention(z, z.clone(), kc, kc, i.view(1, 1), i, i, 64, 1, 128, None, 1.0, None)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (1, 300, 77), (65, 64, 16), (130, 257, 1000), (7, 389, 120)])
+def test_sgemm_true_fp32(M, N, K):
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(8)
+    a, w = torch.randn(M, K), torch.randn(N, K)
+    out = ops.linear(a.to(DEV), w.to(DEV))
+    want = a.double() @ w.double().t()
+    assert float((out.cpu().double() - want).abs().max()) <= 1e-6 * math.sqrt(K) * float(want.abs().max() + 1)
+    # row results do not depend on the other rows of the batch
+    out1 = ops.linear(a[:1].to(DEV), w.to(DEV))
+    assert torch.equal(out1.cpu(), out[:1].cpu())
+    # a strided input (a section of a wider row)
+    wide = torch.randn(M, K + 9).to(DEV)
+    out2 = ops.linear(wide[:, 4: 4 + K], w.to(DEV))
+    assert torch.equal(out2.cpu(), ops.linear(wide[:, 4: 4 + K].contiguous(), w.to(DEV)).cpu())
+
+
+def test_sgemm_keeps_what_tf32_would_lose():
+    """Inputs with 20 significant bits: a reduced-precision matrix mode would round them to 10."""
+    from photon_infer_b200.kernels import ops
+    a = torch.tensor([[1.0 + 2.0 ** -18, 1.0]])
+    w = torch.tensor([[1.0, -1.0]])
+    assert float(ops.linear(a.to(DEV), w.to(DEV)).cpu()[0, 0]) == 2.0 ** -18
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 389, 120), (40, 512, 256), (3, 100, 72)])
+def test_linear_bf16_with_fp32_output(M, N, K):
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(9)
+    a, w = torch.randn(M, K).bfloat16(), torch.randn(N, K).bfloat16()
+    want = a.double() @ w.double().t()
+    out = ops.linear(a.to(DEV), w.to(DEV), out_dtype=torch.float32)
+    assert out.dtype == torch.float32
+    assert float((out.cpu().double() - want).abs().max()) <= 1e-5 * float(want.abs().max())
+    _close(ops.linear(a.to(DEV), w.to(DEV)), want, torch.bfloat16)
+
+
+@pytest.mark.parametrize("V", [5, 389, 1024, 50000, 128256])
+def test_sampling(V):
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(10)
+    rows = 6
+    logits = 3 * torch.randn(rows, V)
+    logits[1, V // 2] = logits[1, V - 1] = logits[1].max() + 1          # a tie: the earlier index wins
+    temps = torch.tensor([0.0, 0.0, 0.8, 0.8, 1.7, 0.3])
+    u = torch.tensor([0.0, 0.0, 0.0, 0.37, 0.999, 0.5])
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.sample(logits.to(DEV), temps.to(DEV), u.to(DEV), out)
+    got = out.cpu().tolist()
+    assert got[0] == int(torch.argmax(logits[0]))
+    assert got[1] == V // 2
+    for r in range(2, rows):
+        p = temperature_probabilities(logits[r], float(temps[r])).double()
+        cdf = torch.cumsum(p, 0)
+        want = inverse_cdf_sample(p.float(), float(u[r]))
+        if got[r] != want:
+            # only a value of u within rounding of a step of the CDF may fall to a neighbour
+            lo = float(cdf[got[r] - 1]) if got[r] > 0 else 0.0
+            assert lo - 1e-5 <= float(u[r]) <= float(cdf[got[r]]) + 1e-5, (r, got[r], want)
+    # greedy without temperatures
+    out2 = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.sample(logits.to(DEV), None, None, out2)
+    assert out2.cpu().tolist() == [int(torch.argmax(logits[r])) if r != 1 else V // 2 for r in range(rows)]
