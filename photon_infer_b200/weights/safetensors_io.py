@@ -82,8 +82,8 @@ class SafetensorsFile:
         buf = memoryview(self._mm)[self.data_start + e.begin: self.data_start + e.end]
         if e.end == e.begin:
             return torch.empty(e.shape, dtype=e.dtype)
-        t = torch.frombuffer(buf, dtype=e.dtype).reshape(e.shape)
-        return t.clone()         # own the bytes; the map may close
+        # a private copy of the bytes: the tensor outlives the map and may be written to
+        return torch.frombuffer(bytearray(buf), dtype=e.dtype).reshape(e.shape)
 
     def close(self) -> None:
         try:

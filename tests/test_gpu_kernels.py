@@ -176,7 +176,7 @@ def test_paged_attention_two_requests(dtype, n_q, n_kv, d, ps, window):
     from photon_infer_b200.kernels import ops
     torch.manual_seed(5)
     lens = [150, 97]
-    pages = 40
+    pages = sum((L + ps - 1) // ps for L in lens) + 5
     qs, ks, vs, outs = [], [], [], []
     kc = vc = None
     tables = []
