@@ -56,7 +56,8 @@ def pages_for(model: CausalLM, options: EngineOptions, max_model_len: int) -> in
         return 1
     free, _total = torch.cuda.mem_get_info(model.device)
     budget = int(free * options.gpu_memory_fraction)
-    tokens = min(budget // per_token, options.max_sequences * max_model_len)
+    # no more than every live request at full length, and no more than 2^20 tokens unless asked for
+    tokens = min(budget // per_token, options.max_sequences * max_model_len, 1 << 20)
     return max(1, tokens // ps)
 
 

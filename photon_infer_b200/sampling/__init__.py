@@ -1,0 +1,3 @@
+from .sampler import Sampler, uniform
+
+__all__ = ["Sampler", "uniform"]

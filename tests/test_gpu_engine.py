@@ -1,0 +1,213 @@
+"""Generation through the Python entry point and the command line, against the plain
+implementation; long decoding; the first tokens of a sequence; preemption."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from helpers import ROOT, TINY, TOL, make_model_folder, plain_logits, random_ids, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    return {name: make_model_folder(str(tmp_path_factory.mktemp(name)), name) for name in TINY}
+
+
+def _options(name, dtype, **kw):
+    from photon_infer_b200 import EngineOptions
+    args = dict(dtype=dtype, block_size=TINY[name]["block_size"], max_cache_tokens=2048, max_sequences=8,
+                chunk_size=16, max_num_batched_tokens=48)
+    args.update(kw)
+    return EngineOptions(**args)
+
+
+def _plain_greedy_checked(folder, prompt, got, dtype):
+    """``got`` must be the greedy continuation, except that a step whose two best logits lie closer than
+    the dtype's tolerance may take either (then the plain side follows the engine's choice)."""
+    from plain.llama_plain import PlainLlama
+    m = PlainLlama.from_folder(folder)
+    ids = list(prompt)
+    for step, tok in enumerate(got):
+        logits = m.logits(ids)[-1]
+        best = int(torch.argmax(logits))
+        if tok != best:
+            gap = float(logits[best] - logits[tok])
+            assert gap <= TOL[dtype] * float(logits.abs().max()), f"token {step}: engine {tok}, plain {best}, gap {gap}"
+        ids.append(tok)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(TINY))
+def test_greedy_generation_through_the_entry_point(folders, name, dtype):
+    from photon_infer_b200 import ContinuousBatchEngine
+    vocab = TINY[name]["config"]["vocab_size"]
+    prompts = [random_ids(n, vocab, seed=n) for n in (5, 9, 17, 41)]
+    engine = ContinuousBatchEngine(folders[name], _options(name, dtype))
+    ids = [engine.add_request(p, max_new_tokens=8, ignore_eos=True) for p in prompts]
+    out = engine.run_until_complete()
+    for rid, p in zip(ids, prompts):
+        assert len(out[rid]) == 8 and engine.result(rid).finish_reason == "length"
+        _plain_greedy_checked(folders[name], p, out[rid], dtype)
+    st = engine.get_stats()
+    assert st.num_finished == 4 and st.prefill_tokens == sum(len(p) for p in prompts)
+    assert engine.runner.cache.free_pages() == [g.num_pages for g in engine.runner.cache.groups]
+    if dtype == "float32":
+        from plain.llama_plain import PlainLlama
+        assert out[ids[0]] == PlainLlama.from_folder(folders[name]).greedy(prompts[0], 8)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(folders, dtype):
+    """300 tokens decoded one by one from a short prompt, past many page edges and past the window."""
+    from photon_infer_b200.engine.loading import build_runner
+    from photon_infer_b200.engine.runner import StepEntry
+    name = "tiny_c"
+    vocab = TINY[name]["config"]["vocab_size"]
+    ids = random_ids(310, vocab, seed=77)
+    runner = build_runner(folders[name], _options(name, dtype, max_cache_tokens=320))
+    runner.cache.add_request("x")
+    got = [runner.step([StepEntry("x", ids[:10], list(range(10)))]).logits.cpu()]
+    for t in ids[10:]:
+        got.append(runner.step([StepEntry("x", [t], [0])]).logits.cpu())
+    runner.check_device_errors()
+    got = torch.cat(got)
+    want = plain_logits(folders[name], ids)
+    assert rel_err(got, want) <= TOL[dtype]
+    # the window group kept only a few pages, the full group all of them
+    held = [g.pages_held("x") for g in runner.cache.groups]
+    assert held[0] <= 24 // 16 + 2 and held[1] == (310 + 15) // 16
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(TINY))
+def test_first_tokens_of_a_sequence(folders, name, dtype):
+    """Positions 0, 1, 2: a single key, no earlier page, the rotation at angle zero."""
+    from photon_infer_b200.engine.loading import build_runner
+    from photon_infer_b200.engine.runner import StepEntry
+    vocab = TINY[name]["config"]["vocab_size"]
+    ids = random_ids(3, vocab, seed=3)
+    runner = build_runner(folders[name], _options(name, dtype))
+    want = plain_logits(folders[name], ids)
+    for cut in ([1, 1, 1], [3], [1, 2], [2, 1]):
+        runner.cache.add_request("f")
+        got, p = [], 0
+        for n in cut:
+            got.append(runner.step([StepEntry("f", ids[p:p + n], list(range(n)))]).logits.cpu())
+            p += n
+        runner.cache.free_request("f")
+        assert rel_err(torch.cat(got), want) <= TOL[dtype], cut
+    runner.check_device_errors()
+
+
+def test_temperature_sampling_is_seeded_and_batch_independent(folders):
+    from photon_infer_b200 import ContinuousBatchEngine
+    from photon_infer_b200.sampling import uniform
+    from plain.llama_plain import PlainLlama, inverse_cdf_sample, temperature_probabilities
+    name = "tiny_b"
+    vocab = TINY[name]["config"]["vocab_size"]
+    prompts = [random_ids(n, vocab, seed=50 + n) for n in (3, 12, 31, 70)]
+
+    def run(order):
+        engine = ContinuousBatchEngine(folders[name], _options(name, "float32"))
+        # request ids follow the order of adding: keep each prompt's id fixed by adding placeholders first
+        ids = {}
+        for i in order:
+            ids[i] = engine.add_request(prompts[i], max_new_tokens=6, temperature=0.8, seed=1234, ignore_eos=True)
+        out = engine.run_until_complete()
+        return {i: (ids[i], out[ids[i]]) for i in order}
+
+    a = run([0, 1, 2, 3])
+    b = run([0, 1, 2, 3])
+    assert a == b                                            # same seed, same tokens
+    # each token is the inverse-CDF pick of the plain probabilities with the same uniform number
+    m = PlainLlama.from_folder(folders[name])
+    for i, (rid, toks) in a.items():
+        seq = list(prompts[i])
+        for k, tok in enumerate(toks):
+            p = temperature_probabilities(m.logits(seq)[-1], 0.8)
+            u = uniform(1234, rid, k)
+            want = inverse_cdf_sample(p, u)
+            if tok != want:
+                cdf = torch.cumsum(p.double(), 0)
+                lo = float(cdf[tok - 1]) if tok > 0 else 0.0
+                assert lo - 1e-5 <= u <= float(cdf[tok]) + 1e-5
+            seq.append(tok)
+    # alone, the first request draws the same tokens as in the batch of four
+    alone = run([0])
+    assert alone[0] == a[0]
+    greedy = ContinuousBatchEngine(folders[name], _options(name, "float32"))
+    g = greedy.add_request(prompts[1], max_new_tokens=6, temperature=0.0, ignore_eos=True)
+    assert greedy.run_until_complete()[g] == m.greedy(prompts[1], 6)
+
+
+def test_preemption_on_the_device_changes_no_token(folders):
+    """With a pool too small for all requests at once some are preempted and computed again;
+    the generated tokens equal those of a run with room for all."""
+    from photon_infer_b200 import ContinuousBatchEngine
+    name = "tiny_a"
+    vocab = TINY[name]["config"]["vocab_size"]
+    prompts = [random_ids(n, vocab, seed=9 + n) for n in (40, 33, 47, 25)]
+
+    def run(tokens):
+        engine = ContinuousBatchEngine(folders[name], _options(name, "float32", max_cache_tokens=tokens))
+        ids = [engine.add_request(p, max_new_tokens=40, ignore_eos=True) for p in prompts]
+        out = engine.run_until_complete()
+        return [out[i] for i in ids], engine.get_stats()
+
+    roomy, st1 = run(4096)
+    tight, st2 = run(192)                                     # 12 pages of 16: not enough for four requests of ~80
+    assert st1.preemptions == 0 and st2.preemptions > 0
+    assert roomy == tight
+
+
+def test_eos_stops_generation(folders):
+    from photon_infer_b200 import ContinuousBatchEngine
+    from plain.llama_plain import PlainLlama
+    name = "tiny_a"
+    m = PlainLlama.from_folder(folders[name])
+    prompt = random_ids(12, 256, seed=4)
+    free_run = m.greedy(prompt, 10)
+    import json
+    cfg = json.load(open(os.path.join(folders[name], "config.json")))
+    cfg["eos_token_id"] = free_run[4]
+    alt = folders[name] + "_eos"
+    os.makedirs(alt, exist_ok=True)
+    json.dump(cfg, open(os.path.join(alt, "config.json"), "w"))
+    if not os.path.exists(os.path.join(alt, "model.safetensors")):
+        os.link(os.path.join(folders[name], "model.safetensors"), os.path.join(alt, "model.safetensors"))
+    engine = ContinuousBatchEngine(alt, _options(name, "float32"))
+    rid = engine.add_request(prompt, max_new_tokens=10)
+    out = engine.run_until_complete()[rid]
+    stop = free_run.index(free_run[4])
+    assert out == free_run[:stop + 1] and engine.result(rid).finish_reason == "eos"
+
+
+def test_bad_prompt_token_is_refused(folders):
+    from photon_infer_b200 import ContinuousBatchEngine, PhotonError
+    engine = ContinuousBatchEngine(folders["tiny_a"], _options("tiny_a", "float32"))
+    with pytest.raises(PhotonError):
+        engine.add_request([1, 256, 3])
+
+
+def test_command_line(folders):
+    name = "tiny_a"
+    prompt = random_ids(9, 256, seed=21)
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "llama_infer"), folders[name], "cuda", "--dtype", "fp32",
+           "--prompt-ids", ",".join(map(str, prompt)), "--prompt-ids", "7 8 9", "--max-new-tokens", "5",
+           "--temperature", "0", "--ignore-eos", "--num-blocks", "32", "--no-quantize"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr
+    lines = [l for l in res.stdout.splitlines() if l.startswith("request")]
+    from plain.llama_plain import PlainLlama
+    m = PlainLlama.from_folder(folders[name])
+    assert lines[0].split(": ")[1].split() == [str(t) for t in m.greedy(prompt, 5)]
+    assert lines[1].split(": ")[1].split() == [str(t) for t in m.greedy([7, 8, 9], 5)]
+    assert "tokens/s" in res.stderr
+    bad = subprocess.run(cmd[:3] + ["cpu"] + cmd[4:], capture_output=True, text=True, timeout=120)
+    assert bad.returncode != 0 and "CUDA only" in bad.stderr
+    bad = subprocess.run(cmd + ["--quantize"], capture_output=True, text=True, timeout=120)
+    assert bad.returncode != 0 and "INT8" in bad.stderr
