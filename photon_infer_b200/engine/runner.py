@@ -52,6 +52,8 @@ class ModelRunner:
         self._copy_done: Optional[torch.cuda.Event] = None
         self.steps = 0
         self.tokens = 0
+        self.h2d_bytes = 0                  # bytes of step inputs copied from pinned host memory
+        self.graph_kernel_launches = 0      # kernels of this package replayed inside CUDA graphs
 
     # ------------------------------------------------------------------ host buffers
     def _staging(self, n: int) -> torch.Tensor:
@@ -144,6 +146,7 @@ class ModelRunner:
                 t += q_lens[s]
             cache.fill_block_table(g, rids, seg(7 + G + g).reshape(S, widths[g]))
         dev = stage[:total].to(self.device, non_blocking=True)
+        self.h2d_bytes += 4 * total
         dseg = lambda i: dev[offs[i]: offs[i] + sizes[i]]
         groups = [GroupView(block_table=dseg(7 + G + g).view(S, widths[g]), slot_mapping=dseg(7 + g),
                             page_size=cache.groups[g].page_size, num_pages=cache.groups[g].num_pages,

@@ -68,53 +68,4 @@ class RotaryEncoding(PositionEncoding):
                           n_q, n_kv, self.head_dim, None)
 
 
-register_position_encoding
-
-
-def inverse_frequencies(head_dim: int, theta: float, scaling: Optional[dict]) -> torch.Tensor:
-    """float64 arithmetic on the host, returned as float32 ``[head_dim / 2]``."""
-    out = []
-    for j in range(head_dim // 2):
-        f = float(theta) ** (-2.0 * j / head_dim)
-        if scaling is not None:
-            factor = float(scaling["factor"])
-            low = float(scaling["low_freq_factor"])
-            high = float(scaling["high_freq_factor"])
-            orig = float(scaling["original_max_position_embeddings"])
-            lam = 2.0 * math.pi / f
-            if lam > orig / low:
-                f = f / factor
-            elif lam >= orig / high:
-                s = (orig / lam - low) / (high - low)
-                f = (1.0 - s) * f / factor + s * f
-        out.append(f)
-    return torch.tensor(out, dtype=torch.float64).to(torch.float32)
-
-
-class RotaryEncoding(PositionEncoding):
-    kernel_modules = ("rope_kv",)
-
-    def __init__(self, head_dim: int, theta: float, scaling: Optional[dict] = None, interleaved: bool = False):
-        if head_dim % 2:
-            raise ValueError("rotary encoding needs an even head_dim")
-        self.head_dim = head_dim
-        self.theta = float(theta)
-        self.scaling = dict(scaling) if scaling else None
-        self.interleaved = bool(interleaved)
-        self.inv_freq_host = inverse_frequencies(head_dim, self.theta, self.scaling)
-        self.inv_freq: Optional[torch.Tensor] = None
-
-    def to_device(self, device) -> None:
-        self.inv_freq = self.inv_freq_host.to(device)
-
-    def apply(self, q, k, positions) -> None:
-        """``q`` and ``k`` must be the first two sections of one fused ``[T, (n_q + 2 n_kv) d]``
-        buffer; this entry point is given that buffer with the head counts."""
-        raise NotImplementedError("use apply_fused")
-
-    def apply_fused(self, qkv: torch.Tensor, positions: torch.Tensor, n_q: int, n_kv: int) -> None:
-        ops.rope_kv_write(qkv, positions, self.inv_freq, self.interleaved, None, None, None,
-                          n_q, n_kv, self.head_dim, None)
-
-
 register_position_encoding("rotary", RotaryEncoding)
