@@ -157,14 +157,24 @@ def load_module(module: str, defines: Optional[Dict[str, object]] = None,
         return _loaded[key]
 
 
-def ensure_built(modules: Iterable[str]) -> None:
-    """Compile several modules at once (``nvcc`` processes run side by side)."""
-    todo = [m for m in dict.fromkeys(modules) if not os.path.isfile(library_path(m))]
+def ensure_built(modules: Iterable[object]) -> None:
+    """Compile several modules at once (``nvcc`` processes run side by side).  An item is a module
+    name or a pair (name, definitions) for a module specialised with ``-D``."""
+    todo = []
+    for m in modules:
+        name, defines = (m, None) if isinstance(m, str) else (m[0], dict(m[1]) if m[1] else None)
+        key = (name, tuple(sorted((defines or {}).items())))
+        if key not in [k for k, _, _ in todo] and not os.path.isfile(library_path(name, defines)):
+            todo.append((key, name, defines))
     if not todo:
         return
     with ThreadPoolExecutor(max_workers=min(8, len(todo))) as pool:
-        list(pool.map(compile_module, todo))
+        list(pool.map(lambda item: compile_module(item[1], item[2]), todo))
+
+
+# specialisations that the build check compiles besides the plain modules (the Llama 3.2 1B shape)
+DEFAULT_SPECIALISATIONS = (("attention_decode", {"HEAD_DIM": 64, "GROUP": 4}),)
 
 
 def build_all(verbose: bool = False) -> None:
-    ensure_built(ALL_MODULES)
+    ensure_built(list(ALL_MODULES) + list(DEFAULT_SPECIALISATIONS))

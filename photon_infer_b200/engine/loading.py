@@ -71,4 +71,4 @@ def build_runner(folder: str, options: EngineOptions) -> ModelRunner:
     options.validate()
     model = load_model(folder, options.dtype, options.device)
     mml = options.max_model_len or model.spec.max_position
-    return ModelRunner(model, build_cache(model, options, mml), mml)
+    return ModelRunner(model, build_cache(model, options, mml), mml, use_cuda_graphs=options.use_cuda_graphs)

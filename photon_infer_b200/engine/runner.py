@@ -34,6 +34,14 @@ class StepResult:
     rows: List[tuple]                   # (request_id, position in the request) of each row
 
 
+@dataclasses.dataclass
+class _DecodeGraph:
+    graph: "torch.cuda.CUDAGraph"
+    static_input: torch.Tensor
+    logits: torch.Tensor
+    kernels: int                        # kernels of this package inside one replay
+
+
 _DEVICE_ERRORS = {1: "token id {1} at token {0} of the step is outside the vocabulary of {2}",
                   2: "token {0} of the step was given cache slot {1}, outside the pool of {2} slots",
                   3: "token {0} of the step needs key {1}, whose block-table entry is {2}",
@@ -41,8 +49,13 @@ _DEVICE_ERRORS = {1: "token id {1} at token {0} of the step is outside the vocab
 
 
 class ModelRunner:
-    def __init__(self, model: CausalLM, cache: CacheManager, max_model_len: Optional[int] = None):
+    def __init__(self, model: CausalLM, cache: CacheManager, max_model_len: Optional[int] = None,
+                 use_cuda_graphs: bool = False, max_graph_batch: int = 256):
         self.model = model
+        self.use_cuda_graphs = use_cuda_graphs
+        self.max_graph_batch = max_graph_batch
+        self._graphs: Dict[tuple, "_DecodeGraph"] = {}
+        self._graph_pool = None
         self.cache = cache
         self.device = model.device
         self.max_model_len = max_model_len or model.spec.max_position
@@ -93,15 +106,23 @@ class ModelRunner:
         for e in entries:
             cache.extend(e.request_id, len(e.tokens))
 
-        ctx, logit_rows, rows = self._build_context(entries)
-        logits = self.model.forward(ctx, self._layer_caches, logit_rows)
+        if self.use_cuda_graphs and len(entries) <= self.max_graph_batch and all(len(e.tokens) == 1 for e in entries):
+            logits, ctx, rows = self._graph_step(entries)
+        else:
+            ctx, logit_rows, rows = self._build_context(entries)
+            logits = self.model.forward(ctx, self._layer_caches, logit_rows)
         for e in entries:
             cache.commit(e.request_id, len(e.tokens))
         self.steps += 1
         self.tokens += ctx.num_tokens
         return StepResult(logits, rows)
 
-    def _build_context(self, entries: Sequence[StepEntry]):
+    def _build_context(self, entries: Sequence[StepEntry], widths: Optional[List[int]] = None,
+                       static_input: Optional[torch.Tensor] = None, bound_context: Optional[int] = None):
+        """Builds every index array of the step in one pinned buffer and copies it to the device once.
+        ``widths``: block-table widths to use (default: what the requests need).  ``static_input``: a
+        device buffer of the same layout to copy into (for a captured graph).  ``bound_context``: the
+        context length that kernels may assume as an upper bound when they size their grids."""
         cache = self.cache
         S = len(entries)
         q_lens = [len(e.tokens) for e in entries]
@@ -109,12 +130,14 @@ class ModelRunner:
         T = sum(q_lens)
         rids = [e.request_id for e in entries]
         n_want = sum(len(e.want) for e in entries)
-        widths = cache.table_width(rids)
+        if widths is None:
+            widths = cache.table_width(rids)
         G = len(cache.groups)
         # layout of the one staging buffer (int32 counts)
         sizes = [T, T, T, S + 1, S, S, n_want] + [T] * G + [S * w for w in widths]
         offs = np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])]).astype(np.int64)
         total = int(offs[-1])
+        self._last_total = total
         if self._copy_done is not None:
             self._copy_done.synchronize()
         stage = self._staging(total)
@@ -145,7 +168,11 @@ class ModelRunner:
                 cache.fill_slot_mapping(g, e.request_id, starts[s], q_lens[s], sm[t:t + q_lens[s]])
                 t += q_lens[s]
             cache.fill_block_table(g, rids, seg(7 + G + g).reshape(S, widths[g]))
-        dev = stage[:total].to(self.device, non_blocking=True)
+        if static_input is not None:
+            dev = static_input
+            dev[:total].copy_(stage[:total], non_blocking=True)
+        else:
+            dev = stage[:total].to(self.device, non_blocking=True)
         self.h2d_bytes += 4 * total
         dseg = lambda i: dev[offs[i]: offs[i] + sizes[i]]
         groups = [GroupView(block_table=dseg(7 + G + g).view(S, widths[g]), slot_mapping=dseg(7 + g),
@@ -157,11 +184,56 @@ class ModelRunner:
             context_lens=dseg(4), state_slots=dseg(5), groups=groups,
             host_query_lens=q_lens, host_context_lens=[a + b for a, b in zip(starts, q_lens)],
             host_start_positions=starts, max_query_len=max(q_lens),
-            max_context_len=max(a + b for a, b in zip(starts, q_lens)), error_flag=self.error_flag)
+            max_context_len=bound_context or max(a + b for a, b in zip(starts, q_lens)), error_flag=self.error_flag)
         # the staging buffer is reused by the next step, which waits for this copy first
         self._copy_done = torch.cuda.Event()
         self._copy_done.record()
         return ctx, dseg(6), rows
+
+    # ------------------------------------------------------------------ decode steps as CUDA graphs
+    def _graph_step(self, entries: Sequence[StepEntry]):
+        """A step of single tokens replays a captured graph: same kernels, one launch.  A graph is
+        captured per (batch size, block-table width, wanted rows); the width is a power of two of
+        pages, so a graph serves until a request outgrows it.  The logits it returns live in the
+        graph's memory and are overwritten by the next step of the same shape."""
+        cache = self.cache
+        rids = [e.request_id for e in entries]
+        widths = []
+        for w in cache.table_width(rids):
+            b = 8
+            while b < w:
+                b *= 2
+            widths.append(b)
+        n_want = sum(len(e.want) for e in entries)
+        key = (len(entries), tuple(widths), n_want)
+        bound = max(w * g.page_size for w, g in zip(widths, cache.groups)) if widths else 1
+        graph = self._graphs.get(key)
+        if graph is None:
+            graph = self._capture(entries, widths, bound)
+            self._graphs[key] = graph
+        ctx, _, rows = self._build_context(entries, widths, graph.static_input, bound)
+        graph.graph.replay()
+        self.graph_kernel_launches += graph.kernels
+        return graph.logits, ctx, rows
+
+    def _capture(self, entries: Sequence[StepEntry], widths: List[int], bound: int) -> "_DecodeGraph":
+        from ..kernels import ops
+        # the layout depends only on (batch, widths, wanted rows): one build gives the buffer's size
+        self._build_context(entries, widths, None, bound)
+        size = self._last_total
+        static_input = torch.zeros(size, dtype=torch.int32, device=self.device)
+        ctx, logit_rows, _ = self._build_context(entries, widths, static_input, bound)
+        # once outside the capture: modules load, cuBLAS makes its workspace
+        self.model.forward(ctx, self._layer_caches, logit_rows)
+        torch.cuda.synchronize()
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        g = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
+        with torch.cuda.graph(g, pool=self._graph_pool):
+            logits = self.model.forward(ctx, self._layer_caches, logit_rows)
+        kernels = ops.launch_count() - before
+        return _DecodeGraph(g, static_input, logits, kernels)
 
     # ------------------------------------------------------------------ errors from the device
     def check_device_errors(self) -> None:

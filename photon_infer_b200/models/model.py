@@ -113,25 +113,24 @@ class CausalLM:
             if hasattr(pe, "to_device"):
                 pe.to_device(self.device)
 
-    def kernel_modules(self) -> List[str]:
-        mods = ["elementwise", "sampling"]
+    def kernel_modules(self) -> List[object]:
+        """What this model launches in this dtype: module names and (name, definitions) pairs."""
+        mods: List[object] = ["elementwise", "sampling"]
         if self.dtype == torch.float32:
             mods.append("gemm_f32")
         for _, part in self._skeleton.named_parts():
-            mods.extend(part.kernel_modules)
-        return list(dict.fromkeys(mods))
+            for m in part.required_kernels(self.dtype):
+                if m not in mods:
+                    mods.append(m)
+        return mods
 
     def step_weight_bytes(self) -> int:
-        """Bytes of weights one step reads: every matrix once, the output head, no embedding rows."""
-        total = self.head.numel() * self.head.element_size()
-        seen = set()
+        """Bytes of weights one step reads: every matrix of every run-list entry once, the output
+        head, no embedding rows."""
+        total = self.head.numel() * self.head.element_size() + self.final_norm.weight_bytes()
         for e in self.spec.run:
-            if e.layer in seen:
-                total += sum(p.weight_bytes() for p in self.blocks[e.layer].parts().values())
-                continue
-            seen.add(e.layer)
             total += sum(p.weight_bytes() for p in self.blocks[e.layer].parts().values())
-        return total + self.final_norm.weight_bytes()
+        return total
 
     # ------------------------------------------------------------------ cache needs
     def cache_needs(self) -> List[Tuple[Optional[PagedCacheSpec], Optional[StateSpec]]]:

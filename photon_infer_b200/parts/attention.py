@@ -25,7 +25,7 @@ from .rope import RotaryEncoding
 
 
 class PagedAttention(Mixer):
-    kernel_modules = ("rope_kv", "attention", "gemm_f32")
+    kernel_modules = ("rope_kv", "attention")
 
     def __init__(self, hidden_size: int, n_q_heads: int, n_kv_heads: int, head_dim: int,
                  position_encoding=None, window: Optional[int] = None, scale: Optional[float] = None):
@@ -38,6 +38,13 @@ class PagedAttention(Mixer):
         self.position_encoding = position_encoding
         self.w_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
+
+    def required_kernels(self, dtype):
+        mods = list(self.kernel_modules)
+        group = self.n_q // self.n_kv
+        if dtype == torch.bfloat16 and ops.decode_attention_supported(dtype, self.head_dim, group):
+            mods.append(("attention_decode", {"HEAD_DIM": self.head_dim, "GROUP": group}))
+        return mods
 
     # -- weights: separate q/k/v in the file, one fused matrix on the device
     def tensor_specs(self) -> List[TensorSpec]:
@@ -90,9 +97,30 @@ class PagedAttention(Mixer):
         return project(attn, self.w_o)
 
     def attend(self, q: torch.Tensor, out: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
+        """bfloat16: the split-key kernel where it is compiled for this head size.  float32 and
+        other sizes: the general kernel, whose sums depend only on a token's position."""
         group = ctx.groups[cache.group]
+        gsize = self.n_q // self.n_kv
+        if q.dtype == torch.bfloat16 and ops.decode_attention_supported(q.dtype, self.head_dim, gsize):
+            T = q.shape[0]
+            keys = ctx.max_context_len if self.window is None else min(self.window, ctx.max_context_len)
+            splits = choose_splits(T * self.n_kv, keys, ops.decode_attention_round(q.dtype, self.head_dim, gsize))
+            scratch = None
+            if splits > 1:
+                scratch = torch.empty(T * self.n_q * splits * (self.head_dim + 2), dtype=torch.float32, device=q.device)
+            ops.decode_attention(q, out, cache.k, cache.v, group.block_table, ctx.token_seq, ctx.positions,
+                                 self.n_q, self.n_kv, self.head_dim, self.window, self.scale, splits, scratch,
+                                 ctx.error_flag)
+            return
         ops.paged_attention(q, out, cache.k, cache.v, group.block_table, ctx.token_seq, ctx.positions,
                             self.n_q, self.n_kv, self.head_dim, self.window, self.scale, ctx.error_flag)
+
+
+def choose_splits(blocks_without_split: int, max_keys: int, round_keys: int, target_blocks: int = 2 * 148) -> int:
+    """Shares of keys per token: enough blocks to fill the 148 SMs twice, no share below one round."""
+    by_fill = -(-target_blocks // max(blocks_without_split, 1))
+    by_keys = -(-max(max_keys, 1) // round_keys)
+    return max(1, min(by_fill, by_keys, 64))
 
 
 register_mixer("full_attention", PagedAttention)

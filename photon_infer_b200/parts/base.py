@@ -112,6 +112,10 @@ class Part:
     #: names of the CUDA modules (files under csrc/) the part launches
     kernel_modules: Tuple[str, ...] = ()
 
+    def required_kernels(self, dtype: torch.dtype) -> List[object]:
+        """Modules to compile before the first step: names, or (name, definitions) pairs."""
+        return list(self.kernel_modules)
+
     def tensor_specs(self) -> List[TensorSpec]:
         return []
 

@@ -14,7 +14,7 @@ from .registry import register_feed_forward
 
 
 class SwiGLUFeedForward(FeedForward):
-    kernel_modules = ("elementwise", "gemm_f32")
+    kernel_modules = ("elementwise",)
 
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden_size = hidden_size
