@@ -115,6 +115,8 @@ def main() -> int:
     ap.add_argument("--block-size", type=int, default=16)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="run one phase only (for profiling); the JSON line then lacks the other figures")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -181,11 +183,13 @@ def main() -> int:
         kv_bytes = cache.cached_bytes([("d", i) for i in range(batch)])
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0 = time.monotonic()
+        torch.cuda.profiler.start()          # for `ncu --profile-from-start off`; no effect otherwise
         e0.record()
         for k in range(warmup, warmup + steps):
             one(k)
         e1.record()
         torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
         t1 = time.monotonic()
         ms = e0.elapsed_time(e1)
         kv_bytes = (kv_bytes + cache.cached_bytes([("d", i) for i in range(batch)])) // 2
@@ -198,17 +202,21 @@ def main() -> int:
     # ---- prefill of 2,048 tokens (one request, one step), timed alone
     prompt = rand_ids(PREFILL_TOKENS)
     pf_ms = []
-    for rep in range(4):
+    for rep in range(4 if args.only != "decode" else 0):
         cache.add_request("p")
         torch.cuda.synchronize()
+        if rep == 3 and args.only == "prefill":
+            torch.cuda.profiler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         runner.step([StepEntry("p", prompt, [PREFILL_TOKENS - 1])])
         e1.record()
         torch.cuda.synchronize()
+        if rep == 3 and args.only == "prefill":
+            torch.cuda.profiler.stop()
         pf_ms.append(e0.elapsed_time(e1))
         cache.free_request("p")
-    prefill_ms = min(pf_ms[1:])
+    prefill_ms = min(pf_ms[1:]) if pf_ms else float("nan")
     H, I, L, d = cfg["hidden_size"], cfg["intermediate_size"], args.layers, cfg["head_dim"]
     nq, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
     per_token = 2 * (H * (nq + 2 * nkv) * d + nq * d * H + 3 * H * I)
@@ -217,12 +225,22 @@ def main() -> int:
     prefill = {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
                "ms": round(prefill_ms, 3), "frac": round(prefill_flops / (prefill_ms / 1e3) / (tf_peak * 1e12), 4)}
 
+    if args.only == "prefill":
+        clocks.stop()
+        print(json.dumps({"only": "prefill", "prefill": prefill}))
+        return 0
     # ---- the headline: decode at --batch
     ms_step, kv_bytes, launches, (t0, t1) = decode_region(args.batch, args.steps, args.warmup)
     clock_info = clocks.window(t0, t1)
     value = args.batch / (ms_step / 1e3)
     step_bytes = model.step_weight_bytes() + kv_bytes
     achieved = step_bytes / (ms_step / 1e3) / 1e9
+    if args.only == "decode":
+        clocks.stop()
+        print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": round(ms_step, 4),
+                          "value": round(value, 1), "roofline_frac": round(achieved / hbm_peak, 4),
+                          "gpu_launches": launches}))
+        return 0
     points = {}
     if not args.no_points:
         for b in (1, 64):

@@ -268,6 +268,64 @@ def decode_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
 
 # ----------------------------------------------------------------------------- matrix products
 
+SKINNY_MAX_ROWS = 8         # up to this many rows the weight-streaming kernel runs instead of the library
+
+
+def skinny_gemm_supported(x: torch.Tensor, weight: torch.Tensor, swiglu: bool = False) -> bool:
+    M, K = x.shape
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 1 <= M <= (32 if swiglu else 64)
+            and K % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and weight.is_contiguous()
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+_skinny_buffers = {}
+
+
+def _skinny_scratch(device):
+    """One scratch buffer and one ticket array per device for the split of K over blocks; launches
+    on one stream use them one after the other."""
+    key = (device.type, device.index)
+    if key not in _skinny_buffers:
+        _skinny_buffers[key] = (torch.empty(1 << 20, dtype=torch.float32, device=device),
+                                torch.zeros(8192, dtype=torch.int32, device=device))
+    return _skinny_buffers[key]
+
+
+def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "bf16") -> None:
+    """``out = x @ weight^T`` for few rows, the weights streamed once.  ``epilogue``: ``"bf16"``,
+    ``"f32"`` (float output) or ``"swiglu"`` (``weight`` holds gate rows then up rows; ``out`` is
+    ``[M, I]`` with ``silu(gate) * up``)."""
+    _cuda(x, weight, out)
+    M, K = x.shape
+    N = weight.shape[0]
+    code = {"bf16": 0, "f32": 1, "swiglu": 2}[epilogue]
+    cols = N // 2 if epilogue == "swiglu" else N
+    want = torch.float32 if epilogue == "f32" else torch.bfloat16
+    if not skinny_gemm_supported(x, weight, epilogue == "swiglu") or weight.shape[1] != K:
+        raise PhotonError(ErrorCode.UNSUPPORTED_SIZE, "skinny_gemm: needs bfloat16, K a multiple of 8, aligned rows, few rows of x")
+    if out.shape != (M, cols) or out.dtype != want or out.stride(1) != 1:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, f"skinny_gemm: out must be {want} [{M}, {cols}]")
+    scratch, tickets = _skinny_scratch(x.device)
+    f = _fn("gemm_skinny", "photon_skinny_gemm",
+            [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int, c_void_p, c_long,
+             c_void_p, c_int, c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K, code,
+             _ptr(scratch), scratch.numel(), _ptr(tickets), tickets.numel(), _stream()), "skinny_gemm")
+
+
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(x Wg^T) * (x Wu^T)`` with ``w_gate_up = [Wg; Wu]``: one kernel for few rows, else the
+    product followed by the SwiGLU kernel."""
+    M = x.shape[0]
+    I = w_gate_up.shape[0] // 2
+    out = torch.empty((M, I), dtype=x.dtype, device=x.device)
+    if M <= SKINNY_MAX_ROWS and skinny_gemm_supported(x, w_gate_up, swiglu=True):
+        skinny_gemm(x, w_gate_up, out, "swiglu")
+        return out
+    swiglu(linear(x, w_gate_up), out)
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """``x [M, K] @ weight[N, K]^T``.  float32: this package's FMA kernel (true 32-bit).
@@ -281,6 +339,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = 
     if x.dtype != weight.dtype:
         raise PhotonError(ErrorCode.INVALID_ARGUMENT, f"linear: x is {x.dtype}, weight is {weight.dtype}")
     want = out_dtype or x.dtype
+    if M <= SKINNY_MAX_ROWS and want in (torch.bfloat16, torch.float32) and skinny_gemm_supported(x, weight):
+        if out is None:
+            out = torch.empty((M, N), dtype=want, device=x.device)
+        skinny_gemm(x, weight, out, "f32" if want == torch.float32 else "bf16")
+        return out
     if x.dtype == torch.float32:
         if want != torch.float32:
             raise PhotonError(ErrorCode.INVALID_ARGUMENT, "linear: a float32 product gives float32")

@@ -41,6 +41,8 @@ class PagedAttention(Mixer):
 
     def required_kernels(self, dtype):
         mods = list(self.kernel_modules)
+        if dtype == torch.bfloat16:
+            mods.append("gemm_skinny")
         group = self.n_q // self.n_kv
         if dtype == torch.bfloat16 and ops.decode_attention_supported(dtype, self.head_dim, group):
             mods.append(("attention_decode", {"HEAD_DIM": self.head_dim, "GROUP": group}))

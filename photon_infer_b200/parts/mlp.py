@@ -16,6 +16,9 @@ from .registry import register_feed_forward
 class SwiGLUFeedForward(FeedForward):
     kernel_modules = ("elementwise",)
 
+    def required_kernels(self, dtype):
+        return ["elementwise"] + (["gemm_skinny"] if dtype == torch.bfloat16 else [])
+
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size
@@ -35,9 +38,7 @@ class SwiGLUFeedForward(FeedForward):
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
 
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        gate_up = project(h, self.w_gate_up)
-        act = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
-        ops.swiglu(gate_up, act)
+        act = ops.linear_swiglu(h, self.w_gate_up)
         return project(act, self.w_down)
 
 
