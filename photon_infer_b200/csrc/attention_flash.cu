@@ -1,0 +1,436 @@
+// Paged causal attention on the tensor cores, for bfloat16 and head sizes that are a
+// multiple of 16 up to 128: prompt portions and decoded tokens alike.
+//
+// The query rows of one request that share a key/value head are packed into one matrix:
+// row = token_in_step * GROUP + head_in_group, so the GROUP heads that read the same keys
+// read them once.  Keys and values stream from the paged cache into shared memory in
+// tiles of 64 keys through a ring of cp.async stages (the block table is followed per
+// key row, 16 bytes per copy); scores and the weighted sum run as mma.m16n8k16 with
+// 32-bit accumulation, the softmax is a running one in 32-bit.
+//
+// Two shapes of work, chosen per request by its number of rows:
+//   ROWS  many rows (prompt portions): a block owns 64 rows, each warp 16 of them, all
+//         warps walk the same key tiles; keys after a row's own position are masked.
+//   KEYS  at most 16 rows (decoded tokens): a block owns all rows, every warp takes a
+//         quarter of each key tile, the keys of the request may be split over several
+//         blocks; partial results are merged in a fixed order (shared memory inside a
+//         block, a scratch buffer and a ticket between blocks).
+//
+// Formula: include/photon/ops/kernels/mha_kernel.hpp:188-229 (scores (q.k)/sqrt(d) for the
+// keys up to the token's own position, softmax exp(s-max)/sum, weighted sum of values;
+// head h uses key/value head h / (n_q/n_kv)), with an optional window.  The reference has
+// no tensor-core kernel and no causal mask inside a portion (src/ops/kernels/cuda/
+// paged_attention.cu:90-194, src/arch/transformer_block.cpp:486-509).
+//
+// Compiled per model with -DHEAD_DIM=<d>.
+#include "common.cuh"
+#include <math.h>
+
+#ifndef HEAD_DIM
+#define HEAD_DIM 64
+#endif
+
+#define FA_THREADS 128
+#define FA_TILE_K 64                      // keys per tile
+#define FA_ROWS 64                        // rows per block in ROWS mode
+#define FA_STAGES 3
+#define FA_LD (HEAD_DIM + 8)              // padded row length in shared memory (elements): conflict-free ldmatrix
+#define FA_KD (HEAD_DIM / 16)             // k-steps over the head dimension
+#define FA_ND (HEAD_DIM / 8)              // n-tiles over the head dimension
+
+static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 128, "head size");
+
+__device__ __forceinline__ uint32_t fa_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;           // 0: the 16 bytes are filled with zeros, nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(fa_smem(dst)), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm4(uint32_t* r, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(fa_smem(p)));
+}
+__device__ __forceinline__ void ldsm4t(uint32_t* r, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(fa_smem(p)));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct FlashParams {
+  const bf16* q; long q_stride;           // [T, n_q * d] view
+  bf16* out; long out_stride;             // [T, n_q * d]
+  const bf16* k_cache; const bf16* v_cache;   // [pages, n_kv, page_size, d]
+  const int* block_table; int max_pages;  // [S, max_pages]
+  const int* cu_tokens;                   // [S + 1] first token of each request in the step
+  const int* positions;                   // [T]
+  float* part_acc; float* part_ml; int* tickets;   // scratch of the KEYS mode with splits
+  int n_q, n_kv, group, page_size, num_pages, window, num_splits, tiles_per_seq;
+  float scale_log2;                       // scale * log2(e)
+  int* err;
+};
+
+// Copies the keys [key0, key0 + 64) of key/value head g into one stage (K tile, then V tile).
+// Rows outside [lo, hi] or without a page are filled with zeros.
+__device__ __forceinline__ void load_kv_tile(const FlashParams& P, const int* table, int g, int key0, int lo,
+                                             int hi, bf16* ks, bf16* vs, int t_for_err) {
+  constexpr int CPR = HEAD_DIM / 8;                       // 16-byte chunks per row
+  for (int c = threadIdx.x; c < FA_TILE_K * CPR; c += FA_THREADS) {
+    const int r = c / CPR, cc = c - r * CPR;
+    const int key = key0 + r;
+    bool valid = key >= lo && key <= hi;
+    size_t src = 0;
+    if (valid) {
+      const int page = table[key / P.page_size];
+      if (page < 0 || page >= P.num_pages) {
+        if (cc == 0) report_error(P.err, PHOTON_DEV_BAD_PAGE, t_for_err, key, page);
+        valid = false;
+      } else {
+        src = (((size_t)page * P.n_kv + g) * P.page_size + (key % P.page_size)) * HEAD_DIM + cc * 8;
+      }
+    }
+    cp_async16(ks + r * FA_LD + cc * 8, P.k_cache + src, valid);
+    cp_async16(vs + r * FA_LD + cc * 8, P.v_cache + src, valid);
+  }
+}
+
+// One warp: scores of its 16 rows against NT*8 keys starting at key row `krow` of the K tile, running
+// softmax, weighted sum with the same keys of the V tile.  qa: the rows' A fragments.  pos0/pos1 and
+// lo0/lo1: last and first visible key of the lane's two rows (row lane/4 and lane/4 + 8).
+template <int NT>
+__device__ __forceinline__ void warp_tile(const uint32_t (&qa)[FA_KD][4], const bf16* ks, const bf16* vs, int krow,
+                                          int key_base, int pos0, int pos1, int lo0, int lo1, float scale_log2,
+                                          float (&m)[2], float (&l)[2], float (&o)[FA_ND][4]) {
+  const int lane = threadIdx.x & 31;
+  float s[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+  // S = Q K^T
+#pragma unroll
+  for (int kd = 0; kd < FA_KD; ++kd) {
+#pragma unroll
+    for (int j = 0; j < NT; j += 2) {
+      uint32_t b[4];
+      const int key = krow + j * 8 + (lane & 7) + ((lane >> 4) << 3);
+      const int dim = kd * 16 + (((lane >> 3) & 1) << 3);
+      ldsm4(b, ks + key * FA_LD + dim);
+      mma_bf16(s[j], qa[kd], b[0], b[1]);
+      mma_bf16(s[j + 1], qa[kd], b[2], b[3]);
+    }
+  }
+  // scale, mask, running softmax (base 2)
+  const int c2 = (lane & 3) * 2;
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    const int key = key_base + krow + j * 8 + c2;
+    s[j][0] = (key >= lo0 && key <= pos0) ? s[j][0] * scale_log2 : -INFINITY;
+    s[j][1] = (key + 1 >= lo0 && key + 1 <= pos0) ? s[j][1] * scale_log2 : -INFINITY;
+    s[j][2] = (key >= lo1 && key <= pos1) ? s[j][2] * scale_log2 : -INFINITY;
+    s[j][3] = (key + 1 >= lo1 && key + 1 <= pos1) ? s[j][3] * scale_log2 : -INFINITY;
+    mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+    mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+  }
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+  const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+  const float sub0 = (mn0 == -INFINITY) ? 0.f : mn0, sub1 = (mn1 == -INFINITY) ? 0.f : mn1;
+  const float corr0 = (m[0] == -INFINITY) ? 0.f : exp2f(m[0] - sub0);
+  const float corr1 = (m[1] == -INFINITY) ? 0.f : exp2f(m[1] - sub1);
+  m[0] = mn0; m[1] = mn1;
+  float sum0 = 0.f, sum1 = 0.f;
+  uint32_t pa[NT / 2][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    const float p0 = exp2f(s[j][0] - sub0), p1 = exp2f(s[j][1] - sub0);
+    const float p2 = exp2f(s[j][2] - sub1), p3 = exp2f(s[j][3] - sub1);
+    sum0 += p0 + p1; sum1 += p2 + p3;
+    pa[j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);
+    pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+  }
+  l[0] = l[0] * corr0 + sum0;             // per-lane partial sums; the quad is added up at the end
+  l[1] = l[1] * corr1 + sum1;
+#pragma unroll
+  for (int n = 0; n < FA_ND; ++n) { o[n][0] *= corr0; o[n][1] *= corr0; o[n][2] *= corr1; o[n][3] *= corr1; }
+  // O += P V
+#pragma unroll
+  for (int kk = 0; kk < NT / 2; ++kk) {
+#pragma unroll
+    for (int n = 0; n < FA_ND; n += 2) {
+      uint32_t b[4];
+      const int key = krow + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+      const int dim = n * 8 + ((lane >> 4) << 3);
+      ldsm4t(b, vs + key * FA_LD + dim);
+      mma_bf16(o[n], pa[kk], b[0], b[1]);
+      mma_bf16(o[n + 1], pa[kk], b[2], b[3]);
+    }
+  }
+}
+
+template <bool KEYS_MODE>
+__global__ void __launch_bounds__(FA_THREADS)
+flash_attention_kernel(const FlashParams P) {
+  extern __shared__ __align__(16) unsigned char fa_dyn[];
+  bf16* qs = reinterpret_cast<bf16*>(fa_dyn);                              // FA_ROWS x FA_LD
+  bf16* kv = qs + FA_ROWS * FA_LD;                                         // FA_STAGES x (K | V) x 64 x FA_LD
+  __shared__ int s_flag;
+
+  const int split = blockIdx.x, g = blockIdx.y;
+  const int seq = blockIdx.z / P.tiles_per_seq, qtile = blockIdx.z - seq * P.tiles_per_seq;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int G = P.group;
+  const int tok0 = P.cu_tokens[seq], ntok = P.cu_tokens[seq + 1] - tok0;
+  const int rows = ntok * G;
+  if ((rows <= 16) != KEYS_MODE) return;                                   // the other launch takes this request
+  const int row0 = KEYS_MODE ? 0 : qtile * FA_ROWS;
+  if (row0 >= rows || (KEYS_MODE && qtile > 0)) return;
+  const int nrows = min(KEYS_MODE ? 16 : FA_ROWS, rows - row0);
+  const int* table = P.block_table + (size_t)seq * P.max_pages;
+
+  // positions of the tile's first and last token bound the keys the block needs
+  const int tfirst = row0 / G, tlast = (row0 + nrows - 1) / G;
+  const int pos_first = P.positions[tok0 + tfirst], pos_last = P.positions[tok0 + tlast];
+  const int key_lo = (P.window > 0 && pos_first - P.window + 1 > 0) ? pos_first - P.window + 1 : 0;
+  int tile_begin = key_lo / FA_TILE_K, tile_end = pos_last / FA_TILE_K + 1;     // key tiles [begin, end)
+  if (KEYS_MODE && P.num_splits > 1) {
+    const int per = (tile_end - tile_begin + P.num_splits - 1) / P.num_splits;
+    tile_begin += split * per;
+    tile_end = min(tile_end, tile_begin + per);
+  }
+  const int ntiles = max(0, tile_end - tile_begin);
+
+  // ---- Q rows into shared memory (zeros beyond the valid rows)
+  {
+    constexpr int CPR = HEAD_DIM / 8;
+    const int qrows = KEYS_MODE ? 16 : FA_ROWS;
+    for (int c = threadIdx.x; c < qrows * CPR; c += FA_THREADS) {
+      const int r = c / CPR, cc = c - r * CPR;
+      const int row = row0 + r;
+      const bool valid = row < rows;
+      const int tk = valid ? row / G : 0, h = valid ? row - tk * G : 0;
+      cp_async16(qs + r * FA_LD + cc * 8,
+                 P.q + (size_t)(tok0 + tk) * P.q_stride + (size_t)(g * G + h) * HEAD_DIM + cc * 8, valid);
+    }
+  }
+  auto stage_k = [&](int st) { return kv + (size_t)st * 2 * FA_TILE_K * FA_LD; };
+  auto stage_v = [&](int st) { return kv + (size_t)st * 2 * FA_TILE_K * FA_LD + FA_TILE_K * FA_LD; };
+  // prologue: the first FA_STAGES - 1 tiles (the Q copy joins the first group)
+#pragma unroll
+  for (int i = 0; i < FA_STAGES - 1; ++i) {
+    if (i < ntiles) load_kv_tile(P, table, g, (tile_begin + i) * FA_TILE_K, key_lo, pos_last, stage_k(i), stage_v(i), tok0);
+    cp_async_commit();
+  }
+
+  // ---- per-lane row data
+  const int wrow = KEYS_MODE ? 0 : warp * 16;                              // first row of the warp inside the tile
+  int pos_r[2], lo_r[2];
+#pragma unroll
+  for (int h2 = 0; h2 < 2; ++h2) {
+    const int row = row0 + wrow + (lane >> 2) + h2 * 8;
+    if (row < rows) {
+      pos_r[h2] = P.positions[tok0 + row / G];
+      lo_r[h2] = (P.window > 0 && pos_r[h2] - P.window + 1 > 0) ? pos_r[h2] - P.window + 1 : 0;
+    } else {
+      pos_r[h2] = -1; lo_r[h2] = 0;                                        // sees nothing
+    }
+  }
+  int warp_pos_max = max(pos_r[0], pos_r[1]);
+#pragma unroll
+  for (int o2 = 16; o2 > 0; o2 >>= 1) warp_pos_max = max(warp_pos_max, __shfl_xor_sync(0xffffffffu, warp_pos_max, o2));
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[FA_ND][4];
+#pragma unroll
+  for (int n = 0; n < FA_ND; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+  uint32_t qa[FA_KD][4];
+
+  for (int i = 0; i < ntiles; ++i) {
+    // keep FA_STAGES - 1 tiles in flight
+    {
+      const int nx = i + FA_STAGES - 1;
+      if (nx < ntiles)
+        load_kv_tile(P, table, g, (tile_begin + nx) * FA_TILE_K, key_lo, pos_last, stage_k(nx % FA_STAGES),
+                     stage_v(nx % FA_STAGES), tok0);
+      cp_async_commit();
+    }
+    cp_async_wait<FA_STAGES - 1>();
+    __syncthreads();
+    if (i == 0) {
+#pragma unroll
+      for (int kd = 0; kd < FA_KD; ++kd)
+        ldsm4(qa[kd], qs + (wrow + (lane & 15)) * FA_LD + kd * 16 + ((lane >> 4) << 3));
+    }
+    const int st = i % FA_STAGES;
+    const int key_base = (tile_begin + i) * FA_TILE_K;
+    if (KEYS_MODE) {
+      // every warp takes 16 keys of the tile
+      if (key_base + warp * 16 <= warp_pos_max)
+        warp_tile<2>(qa, stage_k(st), stage_v(st), warp * 16, key_base, pos_r[0], pos_r[1], lo_r[0], lo_r[1],
+                     P.scale_log2, m, l, o);
+    } else {
+      if (key_base <= warp_pos_max)                                        // tiles after the warp's last row are skipped
+        warp_tile<8>(qa, stage_k(st), stage_v(st), 0, key_base, pos_r[0], pos_r[1], lo_r[0], lo_r[1],
+                     P.scale_log2, m, l, o);
+    }
+    __syncthreads();                                                       // the stage may be overwritten
+  }
+  cp_async_wait<0>();
+
+  // the quad's partial sums
+#pragma unroll
+  for (int h2 = 0; h2 < 2; ++h2) {
+    l[h2] += __shfl_xor_sync(0xffffffffu, l[h2], 1);
+    l[h2] += __shfl_xor_sync(0xffffffffu, l[h2], 2);
+  }
+
+  if (!KEYS_MODE) {
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+      const int row = row0 + wrow + (lane >> 2) + h2 * 8;
+      if (row >= rows) continue;
+      const int tk = row / G, h = row - tk * G;
+      const float inv = l[h2] > 0.f ? 1.f / l[h2] : 0.f;
+      bf16* dst = P.out + (size_t)(tok0 + tk) * P.out_stride + (size_t)(g * G + h) * HEAD_DIM + (lane & 3) * 2;
+#pragma unroll
+      for (int n = 0; n < FA_ND; ++n)
+        *reinterpret_cast<__nv_bfloat162*>(dst + n * 8) = __floats2bfloat162_rn(o[n][h2 * 2] * inv, o[n][h2 * 2 + 1] * inv);
+    }
+    return;
+  }
+
+  // ---- KEYS mode: merge the four warps (each saw a quarter of the keys) through shared memory
+  __syncthreads();                                                         // all warps are done with the ring
+  float* wm = reinterpret_cast<float*>(kv);                                // [4][16]
+  float* wl = wm + 4 * 16;                                                 // [4][16]
+  float* wo = wl + 4 * 16;                                                 // [4][16][HEAD_DIM]
+#pragma unroll
+  for (int h2 = 0; h2 < 2; ++h2) {
+    const int r = (lane >> 2) + h2 * 8;
+    if ((lane & 3) == 0) { wm[warp * 16 + r] = m[h2]; wl[warp * 16 + r] = l[h2]; }
+#pragma unroll
+    for (int n = 0; n < FA_ND; ++n) {
+      wo[(warp * 16 + r) * HEAD_DIM + n * 8 + (lane & 3) * 2] = o[n][h2 * 2];
+      wo[(warp * 16 + r) * HEAD_DIM + n * 8 + (lane & 3) * 2 + 1] = o[n][h2 * 2 + 1];
+    }
+  }
+  __syncthreads();
+  const int n_q = P.n_kv * G;
+  for (int e = threadIdx.x; e < nrows * HEAD_DIM; e += FA_THREADS) {
+    const int r = e / HEAD_DIM, d = e - r * HEAD_DIM;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, wm[w * 16 + r]);
+    float L = 0.f, A = 0.f;
+    if (M != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float mw = wm[w * 16 + r];
+        const float sc = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+        L += wl[w * 16 + r] * sc;
+        A += wo[(w * 16 + r) * HEAD_DIM + d] * sc;
+      }
+    }
+    const int tk = r / G, h = r - tk * G;
+    const int head = g * G + h;
+    if (P.num_splits == 1) {
+      P.out[(size_t)(tok0 + tk) * P.out_stride + (size_t)head * HEAD_DIM + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
+    } else {
+      const size_t slot = ((size_t)(tok0 + tk) * n_q + head) * P.num_splits + split;
+      __stcg(P.part_acc + slot * HEAD_DIM + d, A);
+      if (d == 0) { __stcg(P.part_ml + slot * 2, M); __stcg(P.part_ml + slot * 2 + 1, L); }
+    }
+  }
+  if (P.num_splits == 1) return;
+  // the block that draws the last ticket of (request, key/value head) merges the shares in split order
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_flag = (atomicAdd(P.tickets + (size_t)seq * P.n_kv + g, 1) == P.num_splits - 1);
+  __syncthreads();
+  if (!s_flag) return;
+  __threadfence();
+  if (threadIdx.x == 0) P.tickets[(size_t)seq * P.n_kv + g] = 0;
+  for (int e = threadIdx.x; e < nrows * HEAD_DIM; e += FA_THREADS) {
+    const int r = e / HEAD_DIM, d = e - r * HEAD_DIM;
+    const int tk = r / G, h = r - tk * G;
+    const int head = g * G + h;
+    const size_t base = ((size_t)(tok0 + tk) * n_q + head) * P.num_splits;
+    float M = -INFINITY;
+    for (int s2 = 0; s2 < P.num_splits; ++s2) M = fmaxf(M, __ldcg(P.part_ml + (base + s2) * 2));
+    float L = 0.f, A = 0.f;
+    if (M != -INFINITY) {
+      for (int s2 = 0; s2 < P.num_splits; ++s2) {
+        const float ms = __ldcg(P.part_ml + (base + s2) * 2);
+        const float sc = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+        L += __ldcg(P.part_ml + (base + s2) * 2 + 1) * sc;
+        A += __ldcg(P.part_acc + (base + s2) * HEAD_DIM + d) * sc;
+      }
+    }
+    P.out[(size_t)(tok0 + tk) * P.out_stride + (size_t)head * HEAD_DIM + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
+  }
+}
+
+PHOTON_API int photon_flash_attention_head_dim() { return HEAD_DIM; }
+
+// mode bit 0: launch the ROWS kernel (requests with more than 16 rows); bit 1: the KEYS kernel (at most 16
+// rows = tokens * group).  max_tokens_per_seq bounds the tokens any request brings in this step.
+// Scratch (KEYS mode with num_splits > 1): part_acc float [T * n_q * num_splits * d], part_ml float
+// [T * n_q * num_splits * 2], tickets int [S * n_kv] all zero between launches.  Launches that share scratch
+// must not overlap on the device.
+PHOTON_API int photon_flash_attention(const void* q, long q_stride, void* out, long out_stride, const void* k_cache,
+                                      const void* v_cache, const int* block_table, int max_pages,
+                                      const int* cu_tokens, const int* positions, float* part_acc, float* part_ml,
+                                      int* tickets, int S, int max_tokens_per_seq, int n_q, int n_kv, int d,
+                                      int page_size, int num_pages, int window, float scale, int num_splits,
+                                      int mode, int* err, cudaStream_t stream) {
+  if (S <= 0) return 0;
+  if (d != HEAD_DIM || n_kv <= 0 || n_q % n_kv) return PHOTON_ERR_UNSUPPORTED;
+  if (((uintptr_t)q % 16) || ((size_t)q_stride * 2) % 16 || ((uintptr_t)k_cache % 16) || ((uintptr_t)v_cache % 16))
+    return PHOTON_ERR_ARGUMENT;
+  if (num_splits < 1 || num_splits > 65535 || n_kv > 65535) return PHOTON_ERR_UNSUPPORTED;
+  if (num_splits > 1 && (part_acc == nullptr || part_ml == nullptr || tickets == nullptr)) return PHOTON_ERR_ARGUMENT;
+  FlashParams P;
+  P.q = (const bf16*)q; P.q_stride = q_stride; P.out = (bf16*)out; P.out_stride = out_stride;
+  P.k_cache = (const bf16*)k_cache; P.v_cache = (const bf16*)v_cache;
+  P.block_table = block_table; P.max_pages = max_pages; P.cu_tokens = cu_tokens; P.positions = positions;
+  P.part_acc = part_acc; P.part_ml = part_ml; P.tickets = tickets;
+  P.n_q = n_q; P.n_kv = n_kv; P.group = n_q / n_kv; P.page_size = page_size; P.num_pages = num_pages;
+  P.window = window; P.scale_log2 = scale * 1.4426950408889634f; P.err = err;
+  const size_t smem = ((size_t)FA_ROWS * FA_LD + (size_t)FA_STAGES * 2 * FA_TILE_K * FA_LD) * sizeof(bf16);
+  static bool attr_done = false;
+  if (!attr_done && smem > 48 * 1024) {
+    cudaError_t e1 = cudaFuncSetAttribute(flash_attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e2 = cudaFuncSetAttribute(flash_attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e1 != cudaSuccess) return (int)e1;
+    if (e2 != cudaSuccess) return (int)e2;
+    attr_done = true;
+  }
+  if (mode & 1) {
+    const int rows = max_tokens_per_seq * P.group;
+    P.tiles_per_seq = (rows + FA_ROWS - 1) / FA_ROWS;
+    P.num_splits = 1;
+    if ((long)S * P.tiles_per_seq > 65535) return PHOTON_ERR_UNSUPPORTED;
+    dim3 grid(1, n_kv, S * P.tiles_per_seq);
+    flash_attention_kernel<false><<<grid, FA_THREADS, smem, stream>>>(P);
+    int st = launch_status();
+    if (st != 0) return st;
+  }
+  if (mode & 2) {
+    P.tiles_per_seq = 1;
+    P.num_splits = num_splits;
+    if (S > 65535) return PHOTON_ERR_UNSUPPORTED;
+    dim3 grid(num_splits, n_kv, S);
+    flash_attention_kernel<true><<<grid, FA_THREADS, smem, stream>>>(P);
+    return launch_status();
+  }
+  return 0;
+}

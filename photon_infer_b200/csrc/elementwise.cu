@@ -36,29 +36,78 @@ PHOTON_API int photon_embedding(const int* ids, const void* table, int table_dty
 // residual (float, in place) += delta; out = w * (residual * r).  rows == nullptr: row = blockIdx.x
 // of both residual and out.  rows != nullptr: reads row rows[blockIdx.x] and does NOT write the sum
 // back (the listed rows are only read; out has one row per list entry).
-template <typename TD, typename TO>
+template <typename T> struct Quad;            // four consecutive elements as one load or store
+template <> struct Quad<float> {
+  __device__ static void load(const float* p, float* f) { const float4 r = *reinterpret_cast<const float4*>(p); f[0] = r.x; f[1] = r.y; f[2] = r.z; f[3] = r.w; }
+  __device__ static void store(float* p, const float* f) { *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]); }
+};
+template <> struct Quad<bf16> {
+  __device__ static void load(const bf16* p, float* f) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+  }
+  __device__ static void store(bf16* p, const float* f) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+    uint2 r;
+    r.x = *reinterpret_cast<uint32_t*>(&a);
+    r.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = r;
+  }
+};
+
+// VEC: rows are read and written four elements at a time (H a multiple of 4, aligned pointers).
+template <typename TD, typename TO, bool VEC>
 __global__ void add_rmsnorm_kernel(const TD* __restrict__ delta, float* __restrict__ residual,
                                    const void* __restrict__ w, int w_bf16, TO* __restrict__ out,
                                    const int* __restrict__ rows, int H, float eps) {
   __shared__ float red[32];
-  extern __shared__ float stash[];               // H floats: the summed row
+  extern __shared__ __align__(16) float stash[];               // H floats: the summed row
   const int r = rows ? rows[blockIdx.x] : blockIdx.x;
   float* res = residual + (size_t)r * H;
   const TD* d = delta ? delta + (size_t)r * H : nullptr;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    float v = res[i];
-    if (d) v += to_f32(d[i]);
-    stash[i] = v;
-    ss += v * v;
+  if (VEC) {
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      float v[4], dv[4];
+      Quad<float>::load(res + i, v);
+      if (d) {
+        Quad<TD>::load(d + i, dv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] += dv[e];
+      }
+      Quad<float>::store(stash + i, v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) ss += v[e] * v[e];
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float v = res[i];
+      if (d) v += to_f32(d[i]);
+      stash[i] = v;
+      ss += v * v;
+    }
   }
   ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)H + eps);
   TO* o = out + (size_t)blockIdx.x * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    const float v = stash[i];
-    if (d && !rows) res[i] = v;
-    o[i] = from_f32<TO>(load_w(w, w_bf16, i) * (v * inv));
+  if (VEC) {
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      float v[4], wv[4], y[4];
+      Quad<float>::load(stash + i, v);
+      if (w_bf16) Quad<bf16>::load((const bf16*)w + i, wv); else Quad<float>::load((const float*)w + i, wv);
+      if (d && !rows) Quad<float>::store(res + i, v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) y[e] = wv[e] * (v[e] * inv);
+      Quad<TO>::store(o + i, y);
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      const float v = stash[i];
+      if (d && !rows) res[i] = v;
+      o[i] = from_f32<TO>(load_w(w, w_bf16, i) * (v * inv));
+    }
   }
 }
 
@@ -67,15 +116,23 @@ static int add_rmsnorm_launch(const void* delta, float* residual, const void* w,
                               const int* rows, int n, int H, float eps, cudaStream_t stream) {
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 200 * 1024) return PHOTON_ERR_UNSUPPORTED;
+  const bool vec = (H % 4 == 0) && ((uintptr_t)delta % 16 == 0) && ((uintptr_t)residual % 16 == 0) &&
+                   ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0);
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = vec ? cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO, true>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                        : cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO, false>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   int threads = 128;
   while (threads < 1024 && threads * 4 < H) threads <<= 1;   // depends on H only
-  add_rmsnorm_kernel<TD, TO><<<n, threads, smem, stream>>>((const TD*)delta, residual, w, w_bf16,
-                                                           (TO*)out, rows, H, eps);
+  if (vec)
+    add_rmsnorm_kernel<TD, TO, true><<<n, threads, smem, stream>>>((const TD*)delta, residual, w, w_bf16,
+                                                                   (TO*)out, rows, H, eps);
+  else
+    add_rmsnorm_kernel<TD, TO, false><<<n, threads, smem, stream>>>((const TD*)delta, residual, w, w_bf16,
+                                                                    (TO*)out, rows, H, eps);
   return launch_status();
 }
 

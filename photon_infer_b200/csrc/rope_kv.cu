@@ -13,81 +13,70 @@
 
 // q [T, n_q * d], k and v [T, n_kv * d], each with its own row stride in elements (they are
 // usually three sections of one fused row).  q and k may be null (nothing to rotate),
-// v may be null when nothing is stored.  grid: T, block: 128.  dynamic smem: d floats (cos | sin).
+// v may be null when nothing is stored.
+// One thread per pair of elements: items [0, n_q*d/2) rotate a pair of q in place, the next
+// n_kv*d/2 rotate a pair of k (in place and into the cache), the last n_kv*d/2 copy a pair of v
+// into the cache.  grid: (ceil(items / 128), T), block: 128.  No shared memory, no barrier; a
+// thread computes the sine and cosine of its own angle.
 template <typename T>
-__global__ void rope_kv_write_kernel(T* q, long q_stride, T* k, long k_stride, const T* v, long v_stride,
-                                     const int* __restrict__ positions,
-                                     const float* __restrict__ inv_freq, int interleaved,
-                                     const int* __restrict__ slot_mapping, T* __restrict__ k_cache,
-                                     T* __restrict__ v_cache, int n_q, int n_kv, int d, int page_size,
-                                     long num_slots, int rotate, int write_kv, int* err) {
-  extern __shared__ float cs[];
-  const int t = blockIdx.x;
+__global__ void __launch_bounds__(128)
+rope_kv_write_kernel(T* q, long q_stride, T* k, long k_stride, const T* v, long v_stride,
+                     const int* __restrict__ positions, const float* __restrict__ inv_freq, int interleaved,
+                     const int* __restrict__ slot_mapping, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                     int n_q, int n_kv, int d, int page_size, long num_slots, int rotate, int write_kv,
+                     int* err) {
+  const int t = blockIdx.y;
   const int half = d >> 1;
-  float* cosv = cs;
-  float* sinv = cs + half;
-  if (rotate) {
-    const float pos = (float)positions[t];
-    for (int j = threadIdx.x; j < half; j += blockDim.x) {
-      float s, c;
-      sincosf(pos * inv_freq[j], &s, &c);
-      cosv[j] = c;
-      sinv[j] = s;
-    }
-    __syncthreads();
-  }
-  T* row = q ? q + (size_t)t * q_stride : nullptr;
-  // queries: rotate in place
-  if (rotate && row) {
-    const int pairs = n_q * half;
-    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
-      const int h = p / half, j = p - h * half;
-      const int i0 = interleaved ? h * d + 2 * j : h * d + j;
-      const int i1 = interleaved ? i0 + 1 : i0 + half;
-      const float x0 = to_f32(row[i0]), x1 = to_f32(row[i1]);
-      row[i0] = from_f32<T>(x0 * cosv[j] - x1 * sinv[j]);
-      row[i1] = from_f32<T>(x0 * sinv[j] + x1 * cosv[j]);
-    }
-  }
-  // keys: rotate, then store in the row (so that a caller that does not use the cache sees
-  // them) and in the cache; values: copy
+  const int item = blockIdx.x * blockDim.x + threadIdx.x;
+  const int q_items = q ? n_q * half : 0;
+  const int k_items = k ? n_kv * half : 0;
+  const int v_items = (v && write_kv) ? n_kv * half : 0;
+  if (item >= q_items + k_items + v_items) return;
+
+  int which, local;                       // 0 q, 1 k, 2 v
+  if (item < q_items) { which = 0; local = item; }
+  else if (item < q_items + k_items) { which = 1; local = item - q_items; }
+  else { which = 2; local = item - q_items - k_items; }
+  const int h = local / half, j = local - h * half;
+  const int i0 = (which != 2 && !interleaved) ? j : 2 * j;
+  const int i1 = (which != 2 && !interleaved) ? j + half : 2 * j + 1;
+
   long slot = -1;
-  if (write_kv) {
+  if (which != 0 && write_kv) {
     slot = slot_mapping[t];
     if (slot >= num_slots || slot < -1) {
-      if (threadIdx.x == 0) report_error(err, PHOTON_DEV_BAD_SLOT, t, (int)slot, (int)num_slots);
+      if (local == 0 && which == 1) report_error(err, PHOTON_DEV_BAD_SLOT, t, (int)slot, (int)num_slots);
       slot = -1;
     }
   }
-  const long page = slot >= 0 ? slot / page_size : 0;
-  const int off = slot >= 0 ? (int)(slot - page * page_size) : 0;
-  if (k == nullptr) return;
-  T* krow = k + (size_t)t * k_stride;
-  const T* vrow = v ? v + (size_t)t * v_stride : nullptr;
-  if (vrow == nullptr) slot = -1;
-  const int kpairs = n_kv * half;
-  for (int p = threadIdx.x; p < kpairs; p += blockDim.x) {
-    const int h = p / half, j = p - h * half;
-    const int i0 = interleaved ? 2 * j : j;
-    const int i1 = interleaved ? i0 + 1 : i0 + half;
-    float x0 = to_f32(krow[h * d + i0]), x1 = to_f32(krow[h * d + i1]);
-    T y0, y1;
-    if (rotate) {
-      y0 = from_f32<T>(x0 * cosv[j] - x1 * sinv[j]);
-      y1 = from_f32<T>(x0 * sinv[j] + x1 * cosv[j]);
-      krow[h * d + i0] = y0;
-      krow[h * d + i1] = y1;
-    } else {
-      y0 = krow[h * d + i0];
-      y1 = krow[h * d + i1];
-    }
+  size_t cache_at = 0;
+  if (slot >= 0) {
+    const long page = slot / page_size;
+    const int off = (int)(slot - page * page_size);
+    cache_at = (((size_t)page * n_kv + h) * page_size + off) * d;
+  }
+  if (which == 2) {
     if (slot >= 0) {
-      const size_t base = (((size_t)page * n_kv + h) * page_size + off) * d;
-      k_cache[base + i0] = y0;
-      k_cache[base + i1] = y1;
-      v_cache[base + i0] = vrow[h * d + i0];
-      v_cache[base + i1] = vrow[h * d + i1];
+      const T* vrow = v + (size_t)t * v_stride + (size_t)h * d;
+      v_cache[cache_at + i0] = vrow[i0];
+      v_cache[cache_at + i1] = vrow[i1];
     }
+    return;
+  }
+  T* row = (which == 0 ? q + (size_t)t * q_stride : k + (size_t)t * k_stride) + (size_t)h * d;
+  T y0 = row[i0], y1 = row[i1];
+  if (rotate) {
+    float sn, cs;
+    sincosf((float)positions[t] * inv_freq[j], &sn, &cs);
+    const float x0 = to_f32(y0), x1 = to_f32(y1);
+    y0 = from_f32<T>(x0 * cs - x1 * sn);
+    y1 = from_f32<T>(x0 * sn + x1 * cs);
+    row[i0] = y0;
+    row[i1] = y1;
+  }
+  if (which == 1 && slot >= 0) {
+    k_cache[cache_at + i0] = y0;
+    k_cache[cache_at + i1] = y1;
   }
 }
 
@@ -100,15 +89,17 @@ PHOTON_API int photon_rope_kv_write(void* q, long q_stride, void* k, long k_stri
                                     cudaStream_t stream) {
   if (T <= 0) return 0;
   if (d <= 0 || (d & 1)) return PHOTON_ERR_UNSUPPORTED;
-  const size_t smem = (size_t)d * sizeof(float);
-  if (smem > 48 * 1024) return PHOTON_ERR_UNSUPPORTED;
+  const int items = ((q ? n_q : 0) + (k ? n_kv : 0) + ((v && write_kv) ? n_kv : 0)) * (d / 2);
+  if (items <= 0) return 0;
+  if (T > 65535) return PHOTON_ERR_UNSUPPORTED;
+  dim3 grid((items + 127) / 128, T);
   if (dtype == PHOTON_BF16)
-    rope_kv_write_kernel<bf16><<<T, 128, smem, stream>>>((bf16*)q, q_stride, (bf16*)k, k_stride,
+    rope_kv_write_kernel<bf16><<<grid, 128, 0, stream>>>((bf16*)q, q_stride, (bf16*)k, k_stride,
         (const bf16*)v, v_stride, positions, inv_freq,
         interleaved, slot_mapping, (bf16*)k_cache, (bf16*)v_cache, n_q, n_kv, d, page_size, num_slots,
         rotate, write_kv, err);
   else
-    rope_kv_write_kernel<float><<<T, 128, smem, stream>>>((float*)q, q_stride, (float*)k, k_stride,
+    rope_kv_write_kernel<float><<<grid, 128, 0, stream>>>((float*)q, q_stride, (float*)k, k_stride,
         (const float*)v, v_stride, positions, inv_freq,
         interleaved, slot_mapping, (float*)k_cache, (float*)v_cache, n_q, n_kv, d, page_size, num_slots,
         rotate, write_kv, err);

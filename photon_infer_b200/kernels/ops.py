@@ -212,58 +212,67 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
            "paged_attention")
 
 
-def decode_attention_supported(dtype: torch.dtype, head_dim: int, group: int) -> bool:
-    """Sizes the split-key kernel is compiled for: a key row must be read by a power-of-two
-    number of lanes of a warp with 16-byte loads, and the heads of a group must fit in registers."""
-    per_lane = 8 if dtype == torch.bfloat16 else 4
-    lanes = head_dim // per_lane
-    return (dtype in _DT and head_dim % per_lane == 0 and 1 <= lanes <= 32 and lanes & (lanes - 1) == 0
-            and 1 <= group <= 8)
+_ticket_buffers = {}
 
 
-def decode_attention_round(dtype: torch.dtype, head_dim: int, group: int) -> int:
-    """Keys one block covers per round; a share of keys is a multiple of it."""
-    per_lane = 8 if dtype == torch.bfloat16 else 4
-    return 4 * (32 // (head_dim // per_lane)) * (2 if group > 4 else 4)
+def _attention_tickets(device) -> torch.Tensor:
+    """Zeroed tickets, one per (token, key/value head); the kernel puts them back to zero."""
+    key = (device.type, device.index)
+    if key not in _ticket_buffers:
+        _ticket_buffers[key] = torch.zeros(1 << 16, dtype=torch.int32, device=device)
+    return _ticket_buffers[key]
 
 
-def decode_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
-                     block_table: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
-                     n_q: int, n_kv: int, head_dim: int, window: Optional[int], scale: float, num_splits: int,
-                     scratch: Optional[torch.Tensor], err: Optional[torch.Tensor]) -> None:
-    """Paged attention with the keys of each token split over ``num_splits`` blocks.  ``scratch``:
-    float32, at least ``T * n_q * num_splits * (head_dim + 2)`` elements when ``num_splits > 1``.
-    The module is compiled for this head size and group size at its first use."""
-    _cuda(q, out, k_cache, v_cache, block_table, token_seq, positions, scratch, err)
+def flash_attention_supported(dtype: torch.dtype, head_dim: int) -> bool:
+    """The tensor-core kernel takes bfloat16 and head sizes that are a multiple of 16 up to 128."""
+    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
+
+
+def flash_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    block_table: torch.Tensor, cu_tokens: torch.Tensor, positions: torch.Tensor,
+                    num_seqs: int, max_tokens_per_seq: int, n_q: int, n_kv: int, head_dim: int,
+                    window: Optional[int], scale: float, num_splits: int, scratch: Optional[torch.Tensor],
+                    rows_mode: bool, keys_mode: bool, err: Optional[torch.Tensor]) -> None:
+    """Paged causal attention on the tensor cores.  ``cu_tokens [S + 1]`` gives each request's
+    tokens in the step.  ``rows_mode``: run requests with more than 16 rows (tokens x heads per
+    group); ``keys_mode``: run the others, their keys split over ``num_splits`` blocks.
+    ``scratch``: float32, at least ``T * n_q * num_splits * (head_dim + 2)`` when ``num_splits > 1``."""
+    _cuda(q, out, k_cache, v_cache, block_table, cu_tokens, positions, scratch, err)
     T = q.shape[0]
-    group = n_q // max(n_kv, 1)
-    if n_kv <= 0 or n_q % n_kv or not decode_attention_supported(q.dtype, head_dim, group):
-        raise PhotonError(ErrorCode.UNSUPPORTED_SIZE,
-                          f"decode_attention: head_dim {head_dim} with {group} heads per group in {q.dtype} is not supported")
-    if q.shape[1] != n_q * head_dim or q.stride(1) != 1 or out.shape != (T, n_q * head_dim) or out.stride(1) != 1:
-        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "decode_attention: q and out must be [T, n_q * head_dim]")
-    if q.dtype != out.dtype or q.dtype != k_cache.dtype or q.dtype != v_cache.dtype:
-        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "decode_attention: q, out and the caches must share one dtype")
-    for name, t in (("block_table", block_table), ("token_seq", token_seq), ("positions", positions)):
+    if not flash_attention_supported(q.dtype, head_dim) or n_kv <= 0 or n_q % n_kv:
+        raise PhotonError(ErrorCode.UNSUPPORTED_SIZE, f"flash_attention: head_dim {head_dim} in {q.dtype} is not supported")
+    if q.shape[1] != n_q * head_dim or q.stride(1) != 1 or out.shape != (T, n_q * head_dim) or not out.is_contiguous():
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "flash_attention: q and out must be [T, n_q * head_dim]")
+    if out.dtype != q.dtype or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "flash_attention: q, out and the caches must be bfloat16")
+    for name, t in (("block_table", block_table), ("cu_tokens", cu_tokens), ("positions", positions)):
         _int32(t, name)
-    part_acc = part_ml = None
-    if num_splits > 1:
-        need = T * n_q * num_splits * (head_dim + 2)
+    if cu_tokens.numel() < num_seqs + 1 or block_table.shape[0] < num_seqs:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "flash_attention: cu_tokens and block_table must cover every request")
+    part_acc = part_ml = tickets = None
+    splits = int(num_splits) if keys_mode else 1
+    if splits > 1:
+        need = T * n_q * splits * (head_dim + 2)
         if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need or not scratch.is_contiguous():
-            raise PhotonError(ErrorCode.INVALID_ARGUMENT, f"decode_attention: scratch must hold {need} float32 values")
+            raise PhotonError(ErrorCode.INVALID_ARGUMENT, f"flash_attention: scratch must hold {need} float32 values")
         part_acc = scratch
-        part_ml = scratch[T * n_q * num_splits * head_dim:]
-    f = _fn("attention_decode", "photon_decode_attention",
-            [c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
-            defines={"HEAD_DIM": head_dim, "GROUP": group})
-    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _dtype_code(q), _ptr(k_cache), _ptr(v_cache),
-             _ptr(block_table), block_table.shape[1], _ptr(token_seq), _ptr(positions), _ptr(part_acc), _ptr(part_ml),
-             T, n_q, n_kv, head_dim, k_cache.shape[2], k_cache.shape[0], int(window) if window else 0, float(scale),
-             int(num_splits), _ptr(err), _stream()), "decode_attention")
-    if num_splits > 1:
+        part_ml = scratch[T * n_q * splits * head_dim:]
+        tickets = _attention_tickets(q.device)
+        if tickets.numel() < num_seqs * n_kv:
+            raise PhotonError(ErrorCode.UNSUPPORTED_SIZE, "flash_attention: too many requests for the ticket buffer")
+    mode = (1 if rows_mode else 0) | (2 if keys_mode else 0)
+    f = _fn("attention_flash", "photon_flash_attention",
+            [c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+             c_void_p, c_void_p],
+            defines={"HEAD_DIM": head_dim})
+    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+             block_table.shape[1], _ptr(cu_tokens), _ptr(positions), _ptr(part_acc), _ptr(part_ml), _ptr(tickets),
+             int(num_seqs), int(max_tokens_per_seq), n_q, n_kv, head_dim, k_cache.shape[2], k_cache.shape[0],
+             int(window) if window else 0, float(scale), splits, mode, _ptr(err), _stream()), "flash_attention")
+    if rows_mode and keys_mode:
         global _launch_count
-        _launch_count += 1          # the merge kernel
+        _launch_count += 1
 
 
 # ----------------------------------------------------------------------------- matrix products

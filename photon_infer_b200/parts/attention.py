@@ -43,9 +43,8 @@ class PagedAttention(Mixer):
         mods = list(self.kernel_modules)
         if dtype == torch.bfloat16:
             mods.append("gemm_skinny")
-        group = self.n_q // self.n_kv
-        if dtype == torch.bfloat16 and ops.decode_attention_supported(dtype, self.head_dim, group):
-            mods.append(("attention_decode", {"HEAD_DIM": self.head_dim, "GROUP": group}))
+        if ops.flash_attention_supported(dtype, self.head_dim):
+            mods.append(("attention_flash", {"HEAD_DIM": self.head_dim}))
         return mods
 
     # -- weights: separate q/k/v in the file, one fused matrix on the device
@@ -99,27 +98,32 @@ class PagedAttention(Mixer):
         return project(attn, self.w_o)
 
     def attend(self, q: torch.Tensor, out: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
-        """bfloat16: the split-key kernel where it is compiled for this head size.  float32 and
+        """bfloat16 with a head size the tensor-core kernel is compiled for: that kernel.  float32 and
         other sizes: the general kernel, whose sums depend only on a token's position."""
         group = ctx.groups[cache.group]
         gsize = self.n_q // self.n_kv
-        if q.dtype == torch.bfloat16 and ops.decode_attention_supported(q.dtype, self.head_dim, gsize):
+        if ops.flash_attention_supported(q.dtype, self.head_dim):
+            # tensor cores: requests with many rows walk their keys in one block per 64 rows, requests
+            # with few rows (decoded tokens) split their keys over blocks
             T = q.shape[0]
-            keys = ctx.max_context_len if self.window is None else min(self.window, ctx.max_context_len)
-            splits = choose_splits(T * self.n_kv, keys, ops.decode_attention_round(q.dtype, self.head_dim, gsize))
-            scratch = None
-            if splits > 1:
-                scratch = torch.empty(T * self.n_q * splits * (self.head_dim + 2), dtype=torch.float32, device=q.device)
-            ops.decode_attention(q, out, cache.k, cache.v, group.block_table, ctx.token_seq, ctx.positions,
-                                 self.n_q, self.n_kv, self.head_dim, self.window, self.scale, splits, scratch,
-                                 ctx.error_flag)
+            few = [n * gsize <= 16 for n in ctx.host_query_lens]
+            keys_mode, rows_mode = any(few), not all(few)
+            splits, scratch = 1, None
+            if keys_mode:
+                keys = ctx.max_context_len if self.window is None else min(self.window, ctx.max_context_len)
+                splits = choose_splits(sum(few) * self.n_kv, keys, 64)
+                if splits > 1:
+                    scratch = torch.empty(T * self.n_q * splits * (self.head_dim + 2), dtype=torch.float32, device=q.device)
+            ops.flash_attention(q, out, cache.k, cache.v, group.block_table, ctx.cu_tokens, ctx.positions,
+                                ctx.num_seqs, ctx.max_query_len, self.n_q, self.n_kv, self.head_dim, self.window,
+                                self.scale, splits, scratch, rows_mode, keys_mode, ctx.error_flag)
             return
         ops.paged_attention(q, out, cache.k, cache.v, group.block_table, ctx.token_seq, ctx.positions,
                             self.n_q, self.n_kv, self.head_dim, self.window, self.scale, ctx.error_flag)
 
 
-def choose_splits(blocks_without_split: int, max_keys: int, round_keys: int, target_blocks: int = 2 * 148) -> int:
-    """Shares of keys per token: enough blocks to fill the 148 SMs twice, no share below one round."""
+def choose_splits(blocks_without_split: int, max_keys: int, round_keys: int, target_blocks: int = 370) -> int:
+    """Shares of keys per token: about as many blocks as are resident at once on 148 SMs (one wave), no share below one round."""
     by_fill = -(-target_blocks // max(blocks_without_split, 1))
     by_keys = -(-max(max_keys, 1) // round_keys)
     return max(1, min(by_fill, by_keys, 64))

@@ -347,74 +347,6 @@ def test_sampling(V):
     assert out2.cpu().tolist() == [int(torch.argmax(logits[r])) if r != 1 else V // 2 for r in range(rows)]
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n_q,n_kv,d,ps,window,splits", [
-    (4, 1, 64, 16, None, 1), (4, 1, 64, 16, None, 5), (32, 8, 64, 16, None, 3), (3, 1, 32, 8, None, 4),
-    (8, 1, 128, 16, None, 2), (2, 2, 16, 4, 5, 3), (6, 2, 64, 32, 70, 2), (5, 5, 128, 16, None, 7)])
-def test_decode_attention_split_keys(dtype, n_q, n_kv, d, ps, window, splits):
-    """The split-key kernel on a batch of tokens with very different numbers of keys (1 to 700)."""
-    from photon_infer_b200.kernels import ops
-    if not ops.decode_attention_supported(dtype, d, n_q // n_kv):
-        pytest.skip("size not compiled for this dtype")
-    torch.manual_seed(11)
-    lens = [700, 1, 65, 333]
-    pages = sum((L + ps - 1) // ps for L in lens) + 3
-    kc = torch.full((pages, n_kv, ps, d), float("nan"), dtype=dtype)
-    vc = torch.full_like(kc, float("nan"))
-    perm = torch.randperm(pages, generator=torch.Generator().manual_seed(3)).tolist()
-    width = max((L + ps - 1) // ps for L in lens) + 1
-    table = torch.full((len(lens), width), -1, dtype=torch.int32)
-    qs, want = [], []
-    for i, L in enumerate(lens):
-        q = torch.randn(L, n_q, d).to(dtype)
-        k = torch.randn(L, n_kv, d).to(dtype)
-        v = torch.randn(L, n_kv, d).to(dtype)
-        for lp in range((L + ps - 1) // ps):
-            table[i, lp] = perm.pop()
-        for t in range(L):
-            kc[table[i, t // ps], :, t % ps] = k[t]
-            vc[table[i, t // ps], :, t % ps] = v[t]
-        o = causal_attention(q.double(), k.double(), v.double(), window=window)
-        qs.append(q[-1:]); want.append(o[-1:])
-        if L > 40:                                  # and a token in the middle of the request
-            qs.append(q[39:40]); want.append(o[39:40])
-    tok_seq = torch.tensor([0, 0, 1, 2, 2, 3, 3], dtype=torch.int32)
-    positions = torch.tensor([699, 39, 0, 64, 39, 332, 39], dtype=torch.int32)
-    T = len(positions)
-    q = torch.cat(qs).reshape(T, n_q * d)
-    out = torch.empty(T, n_q * d, dtype=dtype, device=DEV)
-    err = torch.zeros(4, dtype=torch.int32, device=DEV)
-    scratch = torch.full((T * n_q * splits * (d + 2),), float("nan"), device=DEV)
-    ops.decode_attention(q.to(DEV), out, kc.to(DEV), vc.to(DEV), table.to(DEV), tok_seq.to(DEV), positions.to(DEV),
-                         n_q, n_kv, d, window, 1.0 / math.sqrt(d), splits, scratch, err)
-    assert err.cpu().tolist()[0] == 0
-    assert not torch.isnan(out).any()
-    _close(out, torch.cat(want).reshape(T, n_q * d), dtype)
-
-
-def test_decode_attention_far_key_and_window_edge():
-    from photon_infer_b200.kernels import ops
-    torch.manual_seed(12)
-    n_q, n_kv, d, ps, L = 4, 1, 64, 16, 700
-    for far, window in ((0, None), (63, None), (64, None), (640, None), (699, None), (699 - 24, 24), (699 - 23, 24)):
-        q = 0.1 * torch.randn(1, n_q, d)
-        k = 0.1 * torch.randn(L, n_kv, d)
-        v = torch.randn(L, n_kv, d)
-        k[far] = 0
-        k[far, 0, 0] = 40.0
-        q[0, :, 0] = 40.0
-        kc, vc, table = _paged(k.bfloat16(), v.bfloat16(), ps, 50, seed=far)
-        out = torch.empty(1, n_q * d, dtype=torch.bfloat16, device=DEV)
-        scratch = torch.empty(n_q * 4 * (d + 2), device=DEV)
-        ops.decode_attention(q.bfloat16().reshape(1, -1).to(DEV), out, kc.to(DEV), vc.to(DEV),
-                             table.to(torch.int32).reshape(1, -1).to(DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
-                             torch.tensor([L - 1], dtype=torch.int32, device=DEV), n_q, n_kv, d, window,
-                             1.0 / math.sqrt(d), 4, scratch, None)
-        hit = float((out.float().cpu()[0] - v[far, 0].bfloat16().float().repeat(n_q)).abs().max()) < 1e-3
-        visible = window is None or far > L - 1 - window
-        assert hit == visible, (far, window)
-
-
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 17, 32, 33, 64])
 @pytest.mark.parametrize("N,K", [(64, 64), (389, 120), (2048, 2048), (100, 8200), (16, 8)])
 def test_skinny_gemm(M, N, K):
@@ -462,3 +394,89 @@ def test_skinny_gemm_refuses_what_it_cannot_load():
     # the general entry point takes the library path instead and is still right
     got = ops.linear(x, w)
     _close(got, x.cpu().double() @ w.cpu().double().t(), torch.bfloat16)
+
+
+def _flash_case(n_q, n_kv, d, ps, window, lens, steps, splits, seed=21):
+    """Requests of `lens` tokens; `steps[i]` = (first, count) tokens of request i in this step."""
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(seed)
+    dtype = torch.bfloat16
+    pages = sum((L + ps - 1) // ps for L in lens) + 3
+    kc = torch.full((pages, n_kv, ps, d), float("nan"), dtype=dtype)
+    vc = torch.full_like(kc, float("nan"))
+    perm = torch.randperm(pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    width = max((L + ps - 1) // ps for L in lens) + 1
+    table = torch.full((len(lens), width), -1, dtype=torch.int32)
+    qs, want, positions, cu = [], [], [], [0]
+    for i, L in enumerate(lens):
+        q = torch.randn(L, n_q, d).to(dtype)
+        k = torch.randn(L, n_kv, d).to(dtype)
+        v = torch.randn(L, n_kv, d).to(dtype)
+        for lp in range((L + ps - 1) // ps):
+            table[i, lp] = perm.pop()
+        first, count = steps[i]
+        for t in range(first + count):                      # the cache holds what the step can see, nothing later
+            kc[table[i, t // ps], :, t % ps] = k[t]
+            vc[table[i, t // ps], :, t % ps] = v[t]
+        o = causal_attention(q.double(), k.double(), v.double(), window=window)
+        qs.append(q[first:first + count]); want.append(o[first:first + count])
+        positions += list(range(first, first + count))
+        cu.append(cu[-1] + count)
+    T = cu[-1]
+    q = torch.cat(qs).reshape(T, n_q * d)
+    out = torch.full((T, n_q * d), float("nan"), dtype=dtype, device=DEV)
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    G = n_q // n_kv
+    few = [c * G <= 16 for _, c in steps]
+    scratch = torch.full((T * n_q * splits * (d + 2),), float("nan"), device=DEV)
+    ops.flash_attention(q.to(DEV), out, kc.to(DEV), vc.to(DEV), table.to(DEV), torch.tensor(cu, dtype=torch.int32, device=DEV),
+                        torch.tensor(positions, dtype=torch.int32, device=DEV), len(lens), max(c for _, c in steps),
+                        n_q, n_kv, d, window, 1.0 / math.sqrt(d), splits, scratch, not all(few), any(few), err)
+    assert err.cpu().tolist()[0] == 0
+    assert not torch.isnan(out.float()).any()
+    _close(out, torch.cat(want).reshape(T, n_q * d), dtype)
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,ps,window", [
+    (4, 1, 64, 16, None), (32, 8, 64, 16, None), (3, 1, 32, 8, None), (6, 2, 48, 16, 24), (8, 1, 128, 16, None),
+    (2, 2, 16, 4, 5), (5, 5, 80, 32, None), (6, 2, 64, 16, 70)])
+def test_flash_attention_portions_and_single_tokens(n_q, n_kv, d, ps, window):
+    """One launch pair: a long portion from the start, a portion in the middle of a request, a single late
+    token, the first token of a request, and a two-token portion."""
+    lens = [200, 333, 700, 1, 90]
+    steps = [(0, 200), (150, 183), (699, 1), (0, 1), (88, 2)]
+    for splits in (1, 3):
+        _flash_case(n_q, n_kv, d, ps, window, lens, steps, splits)
+
+
+def test_flash_attention_decode_batch_with_splits():
+    lens = [640, 1, 65, 333, 700, 64, 63, 129]
+    steps = [(L - 1, 1) for L in lens]
+    for splits in (1, 2, 5, 11):
+        _flash_case(32, 8, 64, 16, None, lens, steps, splits)
+        _flash_case(8, 2, 128, 8, None, lens, steps, splits)
+
+
+def test_flash_attention_far_key_and_window_edge():
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(22)
+    n_q, n_kv, d, ps, L = 4, 1, 64, 16, 700
+    for far, window, count in ((0, None, 1), (63, None, 1), (64, None, 1), (640, None, 1), (699, None, 1),
+                               (699 - 24, 24, 1), (699 - 23, 24, 1), (0, None, 40), (333, None, 40)):
+        q = 0.1 * torch.randn(count, n_q, d)
+        k = 0.1 * torch.randn(L, n_kv, d)
+        v = torch.randn(L, n_kv, d)
+        k[far] = 0
+        k[far, 0, 0] = 40.0
+        q[:, :, 0] = 40.0
+        kc, vc, table = _paged(k.bfloat16(), v.bfloat16(), ps, 50, seed=far)
+        out = torch.empty(count, n_q * d, dtype=torch.bfloat16, device=DEV)
+        scratch = torch.empty(count * n_q * 4 * (d + 2), device=DEV)
+        G = n_q // n_kv
+        ops.flash_attention(q.bfloat16().reshape(count, -1).to(DEV), out, kc.to(DEV), vc.to(DEV),
+                            table.to(torch.int32).reshape(1, -1).to(DEV), torch.tensor([0, count], dtype=torch.int32, device=DEV),
+                            torch.arange(L - count, L, dtype=torch.int32, device=DEV), 1, count, n_q, n_kv, d, window,
+                            1.0 / math.sqrt(d), 4, scratch, count * G > 16, count * G <= 16, None)
+        hit = float((out.float().cpu()[-1] - v[far, 0].bfloat16().float().repeat(n_q)).abs().max()) < 1e-3
+        visible = window is None or far > L - 1 - window
+        assert hit == visible, (far, window, count)
