@@ -28,7 +28,7 @@ CSRC_DIR = os.path.dirname(os.path.abspath(__file__))
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-shared", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden"]
-ALL_MODULES = ("elementwise", "rope_kv", "attention", "gemm_f32", "gemm_skinny", "sampling")
+ALL_MODULES = ("elementwise", "rope_kv", "attention", "gemm_f32", "gemm_skinny", "gemm_skinny_static", "sampling")
 
 _loaded: Dict[Tuple[str, Tuple[Tuple[str, str], ...]], ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -80,7 +80,9 @@ def _source_hash(module: str, defines: Tuple[Tuple[str, str], ...], extra_flags:
         with open(os.path.join(CSRC_DIR, name), "rb") as f:
             h.update(f.read())
     for name in sorted(os.listdir(CSRC_DIR)):
-        if name.endswith((".cuh", ".h")) and name != "common.cuh":
+        # other headers, and sources that a module may include whole
+        if (name.endswith((".cuh", ".h")) and name != "common.cuh") or \
+                (name.endswith(".cu") and name != f"{module}.cu" and module.startswith(name[:-3])):
             with open(os.path.join(CSRC_DIR, name), "rb") as f:
                 h.update(f.read())
     h.update(repr((ARCH_FLAGS, BASE_FLAGS, defines, extra_flags)).encode())
