@@ -73,7 +73,7 @@ struct FlashParams {
   const int* cu_tokens;                   // [S + 1] first token of each request in the step
   const int* positions;                   // [T]
   float* part_acc; float* part_ml; int* tickets;   // scratch of the KEYS mode with splits
-  int n_q, n_kv, group, page_size, num_pages, window, num_splits, tiles_per_seq;
+  int n_q, n_kv, group, page_size, page_shift, num_pages, window, num_splits, tiles_per_seq;   // page_shift: log2(page_size) or -1
   float scale_log2;                       // scale * log2(e)
   int* err;
 };
@@ -89,12 +89,14 @@ __device__ __forceinline__ void load_kv_tile(const FlashParams& P, const int* ta
     bool valid = key >= lo && key <= hi;
     size_t src = 0;
     if (valid) {
-      const int page = table[key / P.page_size];
+      const int pidx = P.page_shift >= 0 ? (key >> P.page_shift) : key / P.page_size;
+      const int slot = P.page_shift >= 0 ? (key & (P.page_size - 1)) : key - pidx * P.page_size;
+      const int page = table[pidx];
       if (page < 0 || page >= P.num_pages) {
         if (cc == 0) report_error(P.err, PHOTON_DEV_BAD_PAGE, t_for_err, key, page);
         valid = false;
       } else {
-        src = (((size_t)page * P.n_kv + g) * P.page_size + (key % P.page_size)) * HEAD_DIM + cc * 8;
+        src = (((size_t)page * P.n_kv + g) * P.page_size + slot) * HEAD_DIM + cc * 8;
       }
     }
     cp_async16(ks + r * FA_LD + cc * 8, P.k_cache + src, valid);
@@ -404,6 +406,8 @@ PHOTON_API int photon_flash_attention(const void* q, long q_stride, void* out, l
   P.block_table = block_table; P.max_pages = max_pages; P.cu_tokens = cu_tokens; P.positions = positions;
   P.part_acc = part_acc; P.part_ml = part_ml; P.tickets = tickets;
   P.n_q = n_q; P.n_kv = n_kv; P.group = n_q / n_kv; P.page_size = page_size; P.num_pages = num_pages;
+  P.page_shift = -1;
+  for (int sh = 0; sh < 20; ++sh) if ((1 << sh) == page_size) P.page_shift = sh;
   P.window = window; P.scale_log2 = scale * 1.4426950408889634f; P.err = err;
   const size_t smem = ((size_t)FA_ROWS * FA_LD + (size_t)FA_STAGES * 2 * FA_TILE_K * FA_LD) * sizeof(bf16);
   static bool attr_done = false;

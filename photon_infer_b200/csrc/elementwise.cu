@@ -169,15 +169,46 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
   }
 }
 
+// The same, 16 bytes per load: I a multiple of the elements in 16 bytes, aligned pointers.
+template <typename T>
+__global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I, size_t total_vecs) {
+  constexpr int N = 16 / sizeof(T);
+  const int per_row = I / N;
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < total_vecs; idx += stride) {
+    const size_t t = idx / per_row;
+    const int i = (int)(idx - t * per_row) * N;
+    const uint4 gv = *reinterpret_cast<const uint4*>(gate_up + t * 2 * I + i);
+    const uint4 uv = *reinterpret_cast<const uint4*>(gate_up + t * 2 * I + I + i);
+    const T* gp = reinterpret_cast<const T*>(&gv);
+    const T* up = reinterpret_cast<const T*>(&uv);
+    uint4 ov;
+    T* op = reinterpret_cast<T*>(&ov);
+#pragma unroll
+    for (int e = 0; e < N; ++e) {
+      const float g = to_f32(gp[e]);
+      op[e] = from_f32<T>(g / (1.0f + expf(-g)) * to_f32(up[e]));
+    }
+    *reinterpret_cast<uint4*>(out + t * I + i) = ov;
+  }
+}
+
 PHOTON_API int photon_swiglu(const void* gate_up, void* out, int dtype, int T, int I, cudaStream_t stream) {
   const size_t total = (size_t)T * I;
   if (total == 0) return 0;
   const int threads = 256;
-  size_t blocks = (total + threads - 1) / threads;
-  if (blocks > 148 * 32) blocks = 148 * 32;
-  if (dtype == PHOTON_BF16)
-    swiglu_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, total);
-  else
-    swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, total);
+  const int n = dtype == PHOTON_BF16 ? 8 : 4;
+  const bool vec = (I % n == 0) && ((uintptr_t)gate_up % 16 == 0) && ((uintptr_t)out % 16 == 0);
+  const size_t work = vec ? total / n : total;
+  size_t blocks = (work + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == PHOTON_BF16) {
+    if (vec) swiglu_vec_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, work);
+    else swiglu_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, total);
+  } else {
+    if (vec) swiglu_vec_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, work);
+    else swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, total);
+  }
   return launch_status();
 }
