@@ -30,9 +30,12 @@
 #define HEAD_DIM 64
 #endif
 
-#define FA_THREADS 128
 #define FA_TILE_K 64                      // keys per tile
-#define FA_ROWS 64                        // rows per block in ROWS mode
+#ifndef FA_ROWS
+#define FA_ROWS 128                       // rows per block in ROWS mode (16 per warp)
+#endif
+#define FA_KEYS_THREADS 128               // KEYS mode: four warps, 16 keys of every tile each
+#define FA_ROWS_THREADS (FA_ROWS * 2)
 #define FA_STAGES 3
 #define FA_LD (HEAD_DIM + 8)              // padded row length in shared memory (elements): conflict-free ldmatrix
 #define FA_KD (HEAD_DIM / 16)             // k-steps over the head dimension
@@ -83,7 +86,7 @@ struct FlashParams {
 __device__ __forceinline__ void load_kv_tile(const FlashParams& P, const int* table, int g, int key0, int lo,
                                              int hi, bf16* ks, bf16* vs, int t_for_err) {
   constexpr int CPR = HEAD_DIM / 8;                       // 16-byte chunks per row
-  for (int c = threadIdx.x; c < FA_TILE_K * CPR; c += FA_THREADS) {
+  for (int c = threadIdx.x; c < FA_TILE_K * CPR; c += blockDim.x) {
     const int r = c / CPR, cc = c - r * CPR;
     const int key = key0 + r;
     bool valid = key >= lo && key <= hi;
@@ -180,15 +183,16 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qa)[FA_KD][4], const 
 }
 
 template <bool KEYS_MODE>
-__global__ void __launch_bounds__(FA_THREADS)
+__global__ void __launch_bounds__(KEYS_MODE ? FA_KEYS_THREADS : FA_ROWS_THREADS, KEYS_MODE ? 3 : (FA_ROWS >= 128 ? 2 : 3))
 flash_attention_kernel(const FlashParams P) {
   extern __shared__ __align__(16) unsigned char fa_dyn[];
-  bf16* qs = reinterpret_cast<bf16*>(fa_dyn);                              // FA_ROWS x FA_LD
-  bf16* kv = qs + FA_ROWS * FA_LD;                                         // FA_STAGES x (K | V) x 64 x FA_LD
+  bf16* qs = reinterpret_cast<bf16*>(fa_dyn);                              // (KEYS: 16, ROWS: FA_ROWS) x FA_LD
+  bf16* kv = qs + (KEYS_MODE ? 16 : FA_ROWS) * FA_LD;                      // FA_STAGES x (K | V) x 64 x FA_LD
   __shared__ int s_flag;
 
   const int split = blockIdx.x, g = blockIdx.y;
-  const int seq = blockIdx.z / P.tiles_per_seq, qtile = blockIdx.z - seq * P.tiles_per_seq;
+  // row tiles are handed out last-first: the tiles with the most keys to walk start first
+  const int seq = blockIdx.z / P.tiles_per_seq, qtile = P.tiles_per_seq - 1 - (blockIdx.z - seq * P.tiles_per_seq);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int G = P.group;
   const int tok0 = P.cu_tokens[seq], ntok = P.cu_tokens[seq + 1] - tok0;
@@ -215,7 +219,7 @@ flash_attention_kernel(const FlashParams P) {
   {
     constexpr int CPR = HEAD_DIM / 8;
     const int qrows = KEYS_MODE ? 16 : FA_ROWS;
-    for (int c = threadIdx.x; c < qrows * CPR; c += FA_THREADS) {
+    for (int c = threadIdx.x; c < qrows * CPR; c += blockDim.x) {
       const int r = c / CPR, cc = c - r * CPR;
       const int row = row0 + r;
       const bool valid = row < rows;
@@ -327,7 +331,7 @@ flash_attention_kernel(const FlashParams P) {
   }
   __syncthreads();
   const int n_q = P.n_kv * G;
-  for (int e = threadIdx.x; e < nrows * HEAD_DIM; e += FA_THREADS) {
+  for (int e = threadIdx.x; e < nrows * HEAD_DIM; e += blockDim.x) {
     const int r = e / HEAD_DIM, d = e - r * HEAD_DIM;
     float M = -INFINITY;
 #pragma unroll
@@ -361,7 +365,7 @@ flash_attention_kernel(const FlashParams P) {
   if (!s_flag) return;
   __threadfence();
   if (threadIdx.x == 0) P.tickets[(size_t)seq * P.n_kv + g] = 0;
-  for (int e = threadIdx.x; e < nrows * HEAD_DIM; e += FA_THREADS) {
+  for (int e = threadIdx.x; e < nrows * HEAD_DIM; e += blockDim.x) {
     const int r = e / HEAD_DIM, d = e - r * HEAD_DIM;
     const int tk = r / G, h = r - tk * G;
     const int head = g * G + h;
@@ -409,13 +413,20 @@ PHOTON_API int photon_flash_attention(const void* q, long q_stride, void* out, l
   P.page_shift = -1;
   for (int sh = 0; sh < 20; ++sh) if ((1 << sh) == page_size) P.page_shift = sh;
   P.window = window; P.scale_log2 = scale * 1.4426950408889634f; P.err = err;
-  const size_t smem = ((size_t)FA_ROWS * FA_LD + (size_t)FA_STAGES * 2 * FA_TILE_K * FA_LD) * sizeof(bf16);
+  const size_t ring = (size_t)FA_STAGES * 2 * FA_TILE_K * FA_LD;
+  const size_t smem_rows = ((size_t)FA_ROWS * FA_LD + ring) * sizeof(bf16);
+  const size_t smem_keys = ((size_t)16 * FA_LD + ring) * sizeof(bf16);
   static bool attr_done = false;
-  if (!attr_done && smem > 48 * 1024) {
-    cudaError_t e1 = cudaFuncSetAttribute(flash_attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    cudaError_t e2 = cudaFuncSetAttribute(flash_attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (!attr_done) {
+    // room for several blocks per SM: the largest shared-memory carve-out
+    cudaError_t e1 = cudaFuncSetAttribute(flash_attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rows);
+    cudaError_t e2 = cudaFuncSetAttribute(flash_attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_keys);
+    cudaError_t e3 = cudaFuncSetAttribute(flash_attention_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    cudaError_t e4 = cudaFuncSetAttribute(flash_attention_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     if (e1 != cudaSuccess) return (int)e1;
     if (e2 != cudaSuccess) return (int)e2;
+    if (e3 != cudaSuccess) return (int)e3;
+    if (e4 != cudaSuccess) return (int)e4;
     attr_done = true;
   }
   if (mode & 1) {
@@ -424,7 +435,7 @@ PHOTON_API int photon_flash_attention(const void* q, long q_stride, void* out, l
     P.num_splits = 1;
     if ((long)S * P.tiles_per_seq > 65535) return PHOTON_ERR_UNSUPPORTED;
     dim3 grid(1, n_kv, S * P.tiles_per_seq);
-    flash_attention_kernel<false><<<grid, FA_THREADS, smem, stream>>>(P);
+    flash_attention_kernel<false><<<grid, FA_ROWS_THREADS, smem_rows, stream>>>(P);
     int st = launch_status();
     if (st != 0) return st;
   }
@@ -433,7 +444,7 @@ PHOTON_API int photon_flash_attention(const void* q, long q_stride, void* out, l
     P.num_splits = num_splits;
     if (S > 65535) return PHOTON_ERR_UNSUPPORTED;
     dim3 grid(num_splits, n_kv, S);
-    flash_attention_kernel<true><<<grid, FA_THREADS, smem, stream>>>(P);
+    flash_attention_kernel<true><<<grid, FA_KEYS_THREADS, smem_keys, stream>>>(P);
     return launch_status();
   }
   return 0;
