@@ -61,6 +61,8 @@ class ModelRunner:
         self.max_model_len = max_model_len or model.spec.max_position
         self.error_flag = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._layer_caches = cache.layer_caches()
+        from ..kernels import ops as _ops
+        _ops.set_error_word(self.error_flag)
         self._pinned: Optional[torch.Tensor] = None
         self._copy_done: Optional[torch.cuda.Event] = None
         self.steps = 0

@@ -331,15 +331,72 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     if M <= SKINNY_MAX_ROWS and skinny_gemm_supported(x, w_gate_up, swiglu=True):
         skinny_gemm(x, w_gate_up, out, "swiglu")
         return out
+    if gemm_tc_supported(x, w_gate_up) and gemm_tc_tiles(M, 2 * I, swiglu=True) >= TC_MIN_TILES:
+        gemm_tc(x, w_gate_up, out, "swiglu")
+        return out
     swiglu(linear(x, w_gate_up), out)
     return out
+
+
+_error_words = {}
+
+
+def set_error_word(flag: torch.Tensor) -> None:
+    """The int32[4] word in which kernels called without an explicit one report a wait that ran out."""
+    _error_words[(flag.device.type, flag.device.index)] = flag
+
+
+def _error_word(device) -> Optional[torch.Tensor]:
+    return _error_words.get((device.type, device.index))
+
+
+TC_MIN_TILES = 96           # below this many 128 x 256 tiles the tcgen05 product leaves too many SMs idle
+
+
+def gemm_tc_tiles(M: int, N: int, swiglu: bool = False) -> int:
+    """Tiles the tcgen05 product would run; 0 when a tile of 128 rows would be mostly padding."""
+    if M < 128:
+        return 0
+    cols = N // 2 if swiglu else N
+    return -(-M // 128) * -(-cols // (128 if swiglu else 256))
+
+
+def gemm_tc_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """The tcgen05 product takes bfloat16, K a multiple of 8 and 16-byte aligned rows (TMA)."""
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+            and x.stride(1) == 1 and x.stride(0) % 8 == 0 and weight.is_contiguous()
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "bf16",
+            err: Optional[torch.Tensor] = None) -> None:
+    """``out = x @ weight^T`` on the tcgen05 tensor cores (TMA operands, accumulator in tensor memory).
+    ``epilogue``: ``"bf16"``, ``"f32"`` or ``"swiglu"`` (``weight`` holds gate rows then up rows; ``out``
+    is ``[M, I]``)."""
+    _cuda(x, weight, out, err)
+    M, K = x.shape
+    N = weight.shape[0]
+    code = {"bf16": 0, "f32": 1, "swiglu": 2}[epilogue]
+    cols = N // 2 if epilogue == "swiglu" else N
+    want = torch.float32 if epilogue == "f32" else torch.bfloat16
+    if not gemm_tc_supported(x, weight) or weight.shape[1] != K:
+        raise PhotonError(ErrorCode.UNSUPPORTED_SIZE, "gemm_tc: needs bfloat16, K a multiple of 8 and aligned rows")
+    if out.shape != (M, cols) or out.dtype != want or out.stride(1) != 1:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, f"gemm_tc: out must be {want} [{M}, {cols}]")
+    f = _fn("gemm_tc", "photon_gemm_tc",
+            [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    if err is None:
+        err = _error_word(x.device)
+    _check(f(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K, code,
+             _ptr(err), _stream()), "gemm_tc")
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """``x [M, K] @ weight[N, K]^T``.  float32: this package's FMA kernel (true 32-bit).
-    bfloat16: the library product (cuBLAS through torch), where the reference's engine
-    also calls the library (src/ops/kernels/cuda/matmul_dequant_cached.cu:193-207)."""
+    bfloat16: up to 8 rows the weight-streaming kernel; with enough 128 x 256 tiles to fill the
+    GPU the tcgen05 kernel; in between the library product (cuBLAS through torch), where the
+    reference's engine also calls the library (src/ops/kernels/cuda/matmul_dequant_cached.cu:193-207)."""
     _cuda(x, weight, out)
     M, K = x.shape
     N = weight.shape[0]
@@ -352,6 +409,12 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = 
         if out is None:
             out = torch.empty((M, N), dtype=want, device=x.device)
         skinny_gemm(x, weight, out, "f32" if want == torch.float32 else "bf16")
+        return out
+    if want in (torch.bfloat16, torch.float32) and gemm_tc_supported(x, weight) \
+            and gemm_tc_tiles(M, N) >= TC_MIN_TILES and (out is None or out.stride(1) == 1):
+        if out is None:
+            out = torch.empty((M, N), dtype=want, device=x.device)
+        gemm_tc(x, weight, out, "f32" if want == torch.float32 else "bf16")
         return out
     if x.dtype == torch.float32:
         if want != torch.float32:

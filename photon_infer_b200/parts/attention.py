@@ -42,7 +42,7 @@ class PagedAttention(Mixer):
     def required_kernels(self, dtype):
         mods = list(self.kernel_modules)
         if dtype == torch.bfloat16:
-            mods.append("gemm_skinny")
+            mods.extend(["gemm_skinny", "gemm_tc"])
         if ops.flash_attention_supported(dtype, self.head_dim):
             mods.append(("attention_flash", {"HEAD_DIM": self.head_dim}))
         return mods

@@ -480,3 +480,44 @@ def test_flash_attention_far_key_and_window_edge():
         hit = float((out.float().cpu()[-1] - v[far, 0].bfloat16().float().repeat(n_q)).abs().max()) < 1e-3
         visible = window is None or far > L - 1 - window
         assert hit == visible, (far, window, count)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1, 8, 8), (100, 300, 72), (257, 513, 520), (2048, 3072, 2048),
+                                   (333, 389, 120), (4096, 256, 8192)])
+def test_gemm_tcgen05(M, N, K):
+    """The tensor-memory product against float64, with sizes that leave partial tiles on every side."""
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(15)
+    x = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).bfloat16()
+    want = x.double() @ w.double().t()
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_tc(x, w, out32, "f32", err)
+    assert err.cpu().tolist()[0] == 0
+    assert float((out32.double() - want).abs().max()) <= 2e-6 * math.sqrt(K) * float(want.abs().max())
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc(x, w, out, "bf16", err)
+    _close(out, want, torch.bfloat16)
+    # a strided input (a section of wider rows), as the attention output projection gets
+    wide = torch.randn(M, K + 16, device=DEV).bfloat16()
+    out2 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops.gemm_tc(wide[:, 8: 8 + K], w, out2, "f32", err)
+    ref = wide[:, 8: 8 + K].double() @ w.double().t()
+    assert float((out2.double() - ref).abs().max()) <= 2e-6 * math.sqrt(K) * float(ref.abs().max())
+    assert err.cpu().tolist()[0] == 0
+
+
+@pytest.mark.parametrize("M,I,K", [(128, 128, 64), (70, 200, 96), (2048, 8192, 2048), (300, 136, 72)])
+def test_gemm_tcgen05_swiglu(M, I, K):
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(16)
+    x = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(2 * I, K, device=DEV) / math.sqrt(K)).bfloat16()
+    gu = x.double() @ w.double().t()
+    want = swiglu(gu[:, :I], gu[:, I:])
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    ops.gemm_tc(x, w, out, "swiglu", err)
+    assert err.cpu().tolist()[0] == 0
+    _close(out, want, torch.bfloat16)
