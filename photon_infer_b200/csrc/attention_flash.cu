@@ -190,6 +190,8 @@ flash_attention_kernel(const FlashParams P) {
   bf16* kv = qs + (KEYS_MODE ? 16 : FA_ROWS) * FA_LD;                      // FA_STAGES x (K | V) x 64 x FA_LD
   __shared__ int s_flag;
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int split = blockIdx.x, g = blockIdx.y;
   // row tiles are handed out last-first: the tiles with the most keys to walk start first
   const int seq = blockIdx.z / P.tiles_per_seq, qtile = P.tiles_per_seq - 1 - (blockIdx.z - seq * P.tiles_per_seq);
@@ -435,8 +437,7 @@ PHOTON_API int photon_flash_attention(const void* q, long q_stride, void* out, l
     P.num_splits = 1;
     if ((long)S * P.tiles_per_seq > 65535) return PHOTON_ERR_UNSUPPORTED;
     dim3 grid(1, n_kv, S * P.tiles_per_seq);
-    flash_attention_kernel<false><<<grid, FA_ROWS_THREADS, smem_rows, stream>>>(P);
-    int st = launch_status();
+    int st = launch_pdl(flash_attention_kernel<false>, grid, dim3(FA_ROWS_THREADS), smem_rows, stream, P);
     if (st != 0) return st;
   }
   if (mode & 2) {
@@ -444,8 +445,7 @@ PHOTON_API int photon_flash_attention(const void* q, long q_stride, void* out, l
     P.num_splits = num_splits;
     if (S > 65535) return PHOTON_ERR_UNSUPPORTED;
     dim3 grid(num_splits, n_kv, S);
-    flash_attention_kernel<true><<<grid, FA_KEYS_THREADS, smem_keys, stream>>>(P);
-    return launch_status();
+    return launch_pdl(flash_attention_kernel<true>, grid, dim3(FA_KEYS_THREADS), smem_keys, stream, P);
   }
   return 0;
 }

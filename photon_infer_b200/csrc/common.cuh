@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define PHOTON_API extern "C" __attribute__((visibility("default")))
 
@@ -62,3 +63,32 @@ __device__ __forceinline__ float block_sum(float v, float* smem32) {
 }
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
+
+// ---- programmatic dependent launch: a kernel may start while its predecessor in the stream drains.
+// Everything it reads that the predecessor wrote must come after pdl_wait(); a kernel launched with
+// launch_pdl must call pdl_wait() on every path, so that completion stays ordered along the stream.
+// Off unless PHOTON_PDL=1 is set in the environment: measured on B200 inside CUDA graphs, the decode
+// step of the Llama 3.2 1B shape took 1.45 ms with it against 0.95 ms without.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool photon_pdl_enabled() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("PHOTON_PDL"); v = (e != nullptr && e[0] == '1') ? 1 : 0; }
+  return v != 0;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = photon_pdl_enabled() ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaGetLastError();
+}

@@ -59,11 +59,13 @@ template <> struct Quad<bf16> {
 
 // VEC: rows are read and written four elements at a time (H a multiple of 4, aligned pointers).
 template <typename TD, typename TO, bool VEC>
-__global__ void add_rmsnorm_kernel(const TD* __restrict__ delta, float* __restrict__ residual,
-                                   const void* __restrict__ w, int w_bf16, TO* __restrict__ out,
-                                   const int* __restrict__ rows, int H, float eps) {
+__global__ void add_rmsnorm_kernel(const TD* delta, float* residual,          // written by earlier kernels that may
+                                   const void* __restrict__ w, int w_bf16,    // still run when this one starts: no
+                                   TO* out, const int* rows, int H, float eps) {  // read-only path for them
   __shared__ float red[32];
   extern __shared__ __align__(16) float stash[];               // H floats: the summed row
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = rows ? rows[blockIdx.x] : blockIdx.x;
   float* res = residual + (size_t)r * H;
   const TD* d = delta ? delta + (size_t)r * H : nullptr;
@@ -128,12 +130,10 @@ static int add_rmsnorm_launch(const void* delta, float* residual, const void* w,
   int threads = 128;
   while (threads < 1024 && threads * 4 < H) threads <<= 1;   // depends on H only
   if (vec)
-    add_rmsnorm_kernel<TD, TO, true><<<n, threads, smem, stream>>>((const TD*)delta, residual, w, w_bf16,
-                                                                   (TO*)out, rows, H, eps);
-  else
-    add_rmsnorm_kernel<TD, TO, false><<<n, threads, smem, stream>>>((const TD*)delta, residual, w, w_bf16,
-                                                                    (TO*)out, rows, H, eps);
-  return launch_status();
+    return launch_pdl(add_rmsnorm_kernel<TD, TO, true>, dim3(n), dim3(threads), smem, stream, (const TD*)delta,
+                      residual, w, w_bf16, (TO*)out, rows, H, eps);
+  return launch_pdl(add_rmsnorm_kernel<TD, TO, false>, dim3(n), dim3(threads), smem, stream, (const TD*)delta,
+                    residual, w, w_bf16, (TO*)out, rows, H, eps);
 }
 
 // delta may be null (plain norm).  delta_dtype / out_dtype: PHOTON_F32 or PHOTON_BF16.

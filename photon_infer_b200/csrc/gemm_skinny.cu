@@ -40,6 +40,15 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
   return r;
 }
 
+// x is written by the kernel before this one, which may still be running when this kernel starts
+// (programmatic dependent launch): it is read with ordinary loads after the wait, never through
+// the read-only path.
+__device__ __forceinline__ uint4 ld_plain16(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
+  return r;
+}
+
 __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -99,6 +108,10 @@ skinny_gemm_kernel(const bf16* __restrict__ x, long ldx, const bf16* __restrict_
   constexpr int UNROLL = ((RT * MT <= 2) ? 4 : (RT * MT <= 4 ? 2 : 1)) * ((UB && RT * MT <= 1) ? 2 : 1);
   const int full_blocks = min(nblocks, K >> 5);      // k blocks that lie wholly inside K
   int kb = kb0 + warp;
+  // The weights do not depend on the kernel before this one: their first loads are issued, then the
+  // kernel waits for its predecessor (whose output is x), so the wait overlaps the memory latency.
+  pdl_launch_dependents();
+  bool waited = false;
   // whole rounds: every load is issued before the first product, no predicates
   for (; kb + (UNROLL - 1) * SK_WARPS < full_blocks; kb += SK_WARPS * UNROLL) {
     uint4 wa[UNROLL][RT][2], xb[UNROLL][MT];
@@ -109,8 +122,13 @@ skinny_gemm_kernel(const bf16* __restrict__ x, long ldx, const bf16* __restrict_
       for (int r = 0; r < RT; ++r)
 #pragma unroll
         for (int h = 0; h < 2; ++h) wa[u][r][h] = ld_stream16(wrow[r][h] + k);
+    }
+    if (!waited) { pdl_wait(); waited = true; }
 #pragma unroll
-      for (int t = 0; t < MT; ++t) xb[u][t] = __ldg(reinterpret_cast<const uint4*>(xrow[t] + k));
+    for (int u = 0; u < UNROLL; ++u) {
+      const int k = (kb + u * SK_WARPS) * 32 + c * 8;
+#pragma unroll
+      for (int t = 0; t < MT; ++t) xb[u][t] = ld_plain16(xrow[t] + k);
     }
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u)
@@ -131,9 +149,10 @@ skinny_gemm_kernel(const bf16* __restrict__ x, long ldx, const bf16* __restrict_
     for (int r = 0; r < RT; ++r)
 #pragma unroll
       for (int h = 0; h < 2; ++h) wa[r][h] = ok ? ld_stream16(wrow[r][h] + k) : make_uint4(0, 0, 0, 0);
+    if (!waited) { pdl_wait(); waited = true; }
 #pragma unroll
     for (int t = 0; t < MT; ++t)
-      xb[t] = ok ? __ldg(reinterpret_cast<const uint4*>(xrow[t] + k)) : make_uint4(0, 0, 0, 0);
+      xb[t] = ok ? ld_plain16(xrow[t] + k) : make_uint4(0, 0, 0, 0);
 #pragma unroll
     for (int r = 0; r < RT; ++r)
 #pragma unroll
@@ -143,6 +162,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, long ldx, const bf16* __restrict_
       }
   }
 
+  if (!waited) pdl_wait();
   // add the warps' partial sums in warp order
 #pragma unroll
   for (int r = 0; r < RT; ++r)
@@ -219,12 +239,13 @@ static int skinny_launch(const void* x, long ldx, const void* W, long ldw, void*
   if (scratch == nullptr || tickets == nullptr || row_blocks > num_tickets) ks = 1;
   while (ks > 1 && (long)row_blocks * ks * rt * mt_pad * 128 > scratch_floats) ks /= 2;
   dim3 grid(ks, row_blocks);
-#define SK_GO(MT_)                                                                                     \
-  skinny_gemm_kernel<MT_, EPI, 0><<<grid, SK_THREADS, 0, stream>>>((const bf16*)x, ldx, (const bf16*)W, ldw, \
-                                                                   out, ldo, M, N, K, I, scratch, tickets)
+  int st = 0;
+#define SK_GO(MT_)                                                                                        \
+  st = launch_pdl(skinny_gemm_kernel<MT_, EPI, 0>, grid, dim3(SK_THREADS), 0, stream, (const bf16*)x, ldx, \
+                  (const bf16*)W, ldw, out, ldo, M, N, K, I, scratch, tickets)
   if (mt <= 1 && small_grid && EPI != EPI_SWIGLU)
-    skinny_gemm_kernel<1, EPI, 1><<<grid, SK_THREADS, 0, stream>>>((const bf16*)x, ldx, (const bf16*)W, ldw,
-                                                                   out, ldo, M, N, K, I, scratch, tickets);
+    st = launch_pdl(skinny_gemm_kernel<1, EPI, 1>, grid, dim3(SK_THREADS), 0, stream, (const bf16*)x, ldx,
+                    (const bf16*)W, ldw, out, ldo, M, N, K, I, scratch, tickets);
   else if (mt <= 1) SK_GO(1);
   else if (mt <= 2) SK_GO(2);
   else if (mt <= 4) SK_GO(4);
@@ -233,7 +254,7 @@ static int skinny_launch(const void* x, long ldx, const void* W, long ldw, void*
     else return PHOTON_ERR_UNSUPPORTED;
   } else return PHOTON_ERR_UNSUPPORTED;
 #undef SK_GO
-  return launch_status();
+  return st;
 }
 
 // epilogue: 0 bfloat16, 1 float, 2 SwiGLU (W holds 2I rows, out is [M, I]).

@@ -88,6 +88,8 @@ rope_kv_write_vec_kernel(bf16* q, long q_stride, bf16* k, long k_stride, const b
                          const int* __restrict__ slot_mapping, bf16* __restrict__ k_cache,
                          bf16* __restrict__ v_cache, int n_q, int n_kv, int d, int page_size, long num_slots,
                          int rotate, int write_kv, int* err) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.y;
   const int per_head = d >> 4;                               // items per head
   const int item = blockIdx.x * blockDim.x + threadIdx.x;
@@ -174,10 +176,9 @@ PHOTON_API int photon_rope_kv_write(void* q, long q_stride, void* k, long k_stri
   if (dtype == PHOTON_BF16 && d % 16 == 0 && aligned) {
     const int vitems = ((q ? n_q : 0) + (k ? n_kv : 0) + ((v && write_kv) ? n_kv : 0)) * (d / 16);
     dim3 vgrid((vitems + 127) / 128, T);
-    rope_kv_write_vec_kernel<<<vgrid, 128, 0, stream>>>((bf16*)q, q_stride, (bf16*)k, k_stride, (const bf16*)v,
-        v_stride, positions, inv_freq, interleaved, slot_mapping, (bf16*)k_cache, (bf16*)v_cache, n_q, n_kv, d,
-        page_size, num_slots, rotate, write_kv, err);
-    return launch_status();
+    return launch_pdl(rope_kv_write_vec_kernel, vgrid, dim3(128), 0, stream, (bf16*)q, q_stride, (bf16*)k, k_stride,
+                      (const bf16*)v, v_stride, positions, inv_freq, interleaved, slot_mapping, (bf16*)k_cache,
+                      (bf16*)v_cache, n_q, n_kv, d, page_size, num_slots, rotate, write_kv, err);
   }
   if (dtype == PHOTON_BF16)
     rope_kv_write_kernel<bf16><<<grid, 128, 0, stream>>>((bf16*)q, q_stride, (bf16*)k, k_stride,

@@ -103,10 +103,118 @@ sample_kernel(const float* __restrict__ logits, long ld, const float* __restrict
   }
 }
 
+// ---------------------------------------------------------------- two passes for long rows
+// Pass 1: the row is cut into SAMP_CHUNKS spans; block (chunk, row) finds the span's maximum, its first
+// index and, for temperature rows, the sum of exp((l - span max) / T).  Pass 2: one block per row merges
+// the spans in index order and, for temperature rows, walks the one span the target falls into.
+#define SAMP_CHUNKS 32
+#define SAMP_P1_THREADS 256
+
+__global__ void __launch_bounds__(SAMP_P1_THREADS)
+sample_pass1_kernel(const float* __restrict__ logits, long ld, const float* __restrict__ temperature,
+                    float* __restrict__ part, int V) {
+  __shared__ float red[32];
+  const int r = blockIdx.y, c = blockIdx.x;
+  const float* row = logits + (size_t)r * ld;
+  const int span = (V + SAMP_CHUNKS - 1) / SAMP_CHUNKS;
+  const int lo = c * span, hi = min(V, lo + span);
+  float mx;
+  const int am = hi > lo ? lo + block_argmax(row + lo, hi - lo, &mx) : 0;
+  if (hi <= lo) mx = -INFINITY;
+  const float temp = temperature ? temperature[r] : 0.f;
+  float sum = 0.f;
+  if (temp > 0.f && hi > lo) {
+    float s = 0.f;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) s += expf((row[i] - mx) / temp);
+    sum = block_sum(s, red);
+  }
+  if (threadIdx.x == 0) {
+    float* p = part + ((size_t)r * SAMP_CHUNKS + c) * 4;
+    p[0] = mx; p[1] = __int_as_float(am); p[2] = sum; p[3] = 0.f;
+  }
+}
+
+__global__ void __launch_bounds__(SAMP_THREADS)
+sample_pass2_kernel(const float* __restrict__ logits, long ld, const float* __restrict__ temperature,
+                    const float* __restrict__ u, const float* __restrict__ part, int* __restrict__ out, int V) {
+  __shared__ float span_sum[SAMP_THREADS];
+  __shared__ int s_chunk;
+  __shared__ float s_before, s_target, s_max;
+  const int r = blockIdx.x;
+  const float* row = logits + (size_t)r * ld;
+  const float* p = part + (size_t)r * SAMP_CHUNKS * 4;
+  const float temp = temperature ? temperature[r] : 0.f;
+  if (threadIdx.x == 0) {
+    float M = -INFINITY; int am = 0;
+    for (int c = 0; c < SAMP_CHUNKS; ++c) if (p[c * 4] > M) { M = p[c * 4]; am = __float_as_int(p[c * 4 + 1]); }
+    s_max = M;
+    s_chunk = -1;
+    if (!(temp > 0.f)) {
+      out[r] = am;
+    } else {
+      float total = 0.f;
+      for (int c = 0; c < SAMP_CHUNKS; ++c) if (p[c * 4] != -INFINITY) total += p[c * 4 + 2] * expf((p[c * 4] - M) / temp);
+      const float target = u[r] * total;
+      float cum = 0.f; int pick = -1;
+      for (int c = 0; c < SAMP_CHUNKS; ++c) {
+        const float sc = p[c * 4] != -INFINITY ? p[c * 4 + 2] * expf((p[c * 4] - M) / temp) : 0.f;
+        if (sc > 0.f && cum + sc >= target) { pick = c; break; }
+        cum += sc;
+      }
+      if (pick < 0) {                                  // rounding left the total below the target
+        for (int c = SAMP_CHUNKS - 1; c >= 0; --c) if (p[c * 4] != -INFINITY && p[c * 4 + 2] > 0.f) { pick = c; break; }
+        cum = target;                                  // take the last element of that span with weight
+      }
+      s_chunk = pick; s_before = cum; s_target = target;
+      out[r] = am;                                     // replaced below
+    }
+  }
+  __syncthreads();
+  if (s_chunk < 0) return;
+  // inside the chosen span: every thread owns a contiguous piece, pieces are scanned in order
+  const int span = (V + SAMP_CHUNKS - 1) / SAMP_CHUNKS;
+  const int lo = s_chunk * span, hi = min(V, lo + span);
+  const int piece = (hi - lo + SAMP_THREADS - 1) / SAMP_THREADS;
+  const int plo = lo + threadIdx.x * piece, phi = min(hi, plo + piece);
+  float s = 0.f;
+  for (int i = plo; i < phi; ++i) s += expf((row[i] - s_max) / temp);
+  span_sum[threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float cum = s_before;
+    int t = -1;
+    for (int i = 0; i < SAMP_THREADS; ++i) {
+      if (span_sum[i] > 0.f && cum + span_sum[i] >= s_target) { t = i; break; }
+      cum += span_sum[i];
+    }
+    int pick = -1;
+    if (t >= 0) {
+      const int l2 = lo + t * piece, h2 = min(hi, l2 + piece);
+      for (int i = l2; i < h2; ++i) {
+        cum += expf((row[i] - s_max) / temp);
+        if (cum >= s_target) { pick = i; break; }
+      }
+      if (pick < 0) pick = h2 - 1;
+    } else {
+      for (int i = hi - 1; i >= lo; --i) if (expf((row[i] - s_max) / temp) > 0.f) { pick = i; break; }
+    }
+    if (pick >= 0) out[r] = pick;
+  }
+}
+
+// scratch: float [rows * 32 * 4] for rows longer than 16384 (two passes); may be null, then one pass is used.
 PHOTON_API int photon_sample(const float* logits, long ld, const float* temperature, const float* u, int* out,
-                             int rows, int V, cudaStream_t stream) {
+                             int rows, int V, float* scratch, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (V <= 0) return PHOTON_ERR_ARGUMENT;
+  if (scratch != nullptr && V > 16384 && rows <= 65535) {
+    dim3 g1(SAMP_CHUNKS, rows);
+    sample_pass1_kernel<<<g1, SAMP_P1_THREADS, 0, stream>>>(logits, ld, temperature, scratch, V);
+    int st = launch_status();
+    if (st != 0) return st;
+    sample_pass2_kernel<<<rows, SAMP_THREADS, 0, stream>>>(logits, ld, temperature, u, scratch, out, V);
+    return launch_status();
+  }
   sample_kernel<<<rows, SAMP_THREADS, 0, stream>>>(logits, ld, temperature, u, out, V);
   return launch_status();
 }

@@ -452,5 +452,13 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], u: Optiona
     if temperature is not None and (temperature.dtype != torch.float32 or temperature.numel() != rows
                                     or u is None or u.dtype != torch.float32 or u.numel() != rows):
         raise PhotonError(ErrorCode.SHAPE_MISMATCH, "sample: temperature and u must be float32 [rows]")
-    f = _fn("sampling", "photon_sample", [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
-    _check(f(_ptr(logits), logits.stride(0), _ptr(temperature), _ptr(u), _ptr(out), rows, V, _stream()), "sample")
+    scratch = None
+    if V > 16384:
+        # long rows are cut into 32 spans that separate blocks reduce; their results meet here
+        scratch = torch.empty(rows * 32 * 4, dtype=torch.float32, device=logits.device)
+    f = _fn("sampling", "photon_sample", [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(logits), logits.stride(0), _ptr(temperature), _ptr(u), _ptr(out), rows, V, _ptr(scratch), _stream()),
+           "sample")
+    if scratch is not None:
+        global _launch_count
+        _launch_count += 1
