@@ -250,7 +250,7 @@ def main() -> int:
     # ---- end to end through the entry point: host ids in, sampled ids out, every step
     engine = ContinuousBatchEngine(None, options, runner=runner)
     for i in range(args.batch):
-        engine.add_request(rand_ids(PROMPT_LEN), max_new_tokens=args.warmup + args.steps + 1, ignore_eos=True)
+        engine.add_request(rand_ids(PROMPT_LEN), max_new_tokens=args.warmup + args.steps + 16, ignore_eos=True)
     while any(r.num_generated() < 1 for r in engine.scheduler.requests.values()):
         engine.step()
     for _ in range(args.warmup):

@@ -58,7 +58,12 @@ class CacheGroup:
         table = self.tables[rid]
         first = self.first_visible(old_len) // self.page_size
         last = (new_len - 1) // self.page_size
-        return [i for i in range(first, last + 1) if i >= len(table) or table[i] == NO_PAGE]
+        held = len(table)
+        # tokens arrive in order and pages are only given back below the window, so everything from
+        # `first` up to the table's end is held; what is missing lies beyond the table's end
+        if first >= held or table[first] != NO_PAGE:
+            return list(range(max(first, held), last + 1))
+        return [i for i in range(first, last + 1) if i >= held or table[i] == NO_PAGE]
 
     def pages_needed(self, rid, old_len: int, new_len: int) -> int:
         if new_len <= old_len:

@@ -106,8 +106,21 @@ class CacheManager:
             if n > g.pool.num_free:
                 raise PhotonError(ErrorCode.OUT_OF_MEMORY,
                                   f"request {rid!r} needs {n} more cache pages, {g.pool.num_free} of {g.num_pages} are free")
-        for g in self.groups:
-            g.extend(rid, r.length, r.length + n_tokens)
+        for n, g in zip(need, self.groups):
+            if n:
+                g.extend(rid, r.length, r.length + n_tokens)
+
+    def try_extend(self, rid, n_tokens: int) -> bool:
+        """``extend`` that answers False instead of raising when a pool is too small (nothing is taken)."""
+        r = self._requests[rid]
+        need = self.pages_needed(rid, n_tokens)
+        for n, g in zip(need, self.groups):
+            if n > g.pool.num_free:
+                return False
+        for n, g in zip(need, self.groups):
+            if n:
+                g.extend(rid, r.length, r.length + n_tokens)
+        return True
 
     def commit(self, rid, n_tokens: int) -> None:
         """The step that wrote ``n_tokens`` tokens is enqueued: advance the length and give back the

@@ -85,7 +85,7 @@ class ContinuousBatchEngine:
             entries.append(StepEntry(it.request.request_id, tokens, [it.num_tokens - 1] if it.samples else []))
             if it.samples:
                 samplers.append(it.request)
-        result = self.runner.step(entries)
+        result = self.runner.step(entries, pages_taken=True)
         sampled: Dict[int, int] = {}
         if samplers:
             temps = [r.params.temperature for r in samplers]

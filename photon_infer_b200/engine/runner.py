@@ -77,7 +77,8 @@ class ModelRunner:
         return self._pinned
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry]) -> StepResult:
+    def step(self, entries: Sequence[StepEntry], pages_taken: bool = False) -> StepResult:
+        """``pages_taken``: the caller (the scheduler) has already taken the pages these tokens need."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return StepResult(torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device), [])
@@ -97,7 +98,11 @@ class ModelRunner:
                     raise PhotonError(ErrorCode.INVALID_INDEX, f"wanted place {w} is outside the {len(e.tokens)} tokens given")
         # pages first: all or nothing over the whole step
         need = [0] * len(cache.groups)
-        for e in entries:
+        if pages_taken:
+            entries_to_extend = []
+        else:
+            entries_to_extend = entries
+        for e in entries_to_extend:
             for g, n in enumerate(cache.pages_needed(e.request_id, len(e.tokens))):
                 need[g] += n
         for g, n in enumerate(need):
@@ -105,7 +110,7 @@ class ModelRunner:
                 raise PhotonError(ErrorCode.OUT_OF_MEMORY,
                                   f"the step needs {n} more cache pages in group {g}, "
                                   f"{cache.groups[g].pool.num_free} of {cache.groups[g].num_pages} are free")
-        for e in entries:
+        for e in entries_to_extend:
             cache.extend(e.request_id, len(e.tokens))
 
         if self.use_cuda_graphs and len(entries) <= self.max_graph_batch and all(len(e.tokens) == 1 for e in entries):
@@ -146,30 +151,50 @@ class ModelRunner:
         host = stage.numpy()
         seg = lambda i: host[offs[i]: offs[i] + sizes[i]]
         tok, pos, tseq, cu, ctxl, slots, lrows = (seg(i) for i in range(7))
-        t = 0
         rows: List[tuple] = []
-        w = 0
-        for s, e in enumerate(entries):
-            n = q_lens[s]
-            tok[t:t + n] = np.asarray(e.tokens, dtype=np.int64)
-            pos[t:t + n] = np.arange(starts[s], starts[s] + n)
-            tseq[t:t + n] = s
-            cu[s] = t
-            ctxl[s] = starts[s] + n
-            slots[s] = cache.states.slot_of(e.request_id)
-            for k in e.want:
-                lrows[w] = t + k
-                rows.append((e.request_id, starts[s] + k))
-                w += 1
-            t += n
-        cu[S] = T
-        for g in range(G):
-            sm = seg(7 + g)
-            t = 0
+        if T == S:
+            # every request brings one token (a decode step): whole arrays at once
+            tok[:] = [e.tokens[0] for e in entries]
+            pos[:] = starts
+            tseq[:] = range(S)
+            cu[:] = range(S + 1)
+            ctxl[:] = [p + 1 for p in starts]
+            slots[:] = [cache.states.slot_of(r) for r in rids]
+            w = 0
             for s, e in enumerate(entries):
-                cache.fill_slot_mapping(g, e.request_id, starts[s], q_lens[s], sm[t:t + q_lens[s]])
-                t += q_lens[s]
-            cache.fill_block_table(g, rids, seg(7 + G + g).reshape(S, widths[g]))
+                for k in e.want:
+                    lrows[w] = s + k
+                    rows.append((e.request_id, starts[s] + k))
+                    w += 1
+            for g in range(G):
+                grp = cache.groups[g]
+                ps = grp.page_size
+                seg(7 + g)[:] = [grp.tables[r][p // ps] * ps + p % ps for r, p in zip(rids, starts)]
+                cache.fill_block_table(g, rids, seg(7 + G + g).reshape(S, widths[g]))
+        else:
+            t = 0
+            w = 0
+            for s, e in enumerate(entries):
+                n = q_lens[s]
+                tok[t:t + n] = np.asarray(e.tokens, dtype=np.int64)
+                pos[t:t + n] = np.arange(starts[s], starts[s] + n)
+                tseq[t:t + n] = s
+                cu[s] = t
+                ctxl[s] = starts[s] + n
+                slots[s] = cache.states.slot_of(e.request_id)
+                for k in e.want:
+                    lrows[w] = t + k
+                    rows.append((e.request_id, starts[s] + k))
+                    w += 1
+                t += n
+            cu[S] = T
+            for g in range(G):
+                sm = seg(7 + g)
+                t = 0
+                for s, e in enumerate(entries):
+                    cache.fill_slot_mapping(g, e.request_id, starts[s], q_lens[s], sm[t:t + q_lens[s]])
+                    t += q_lens[s]
+                cache.fill_block_table(g, rids, seg(7 + G + g).reshape(S, widths[g]))
         if static_input is not None:
             dev = static_input
             dev[:total].copy_(stage[:total], non_blocking=True)

@@ -154,8 +154,7 @@ class ContinuousBatchScheduler:
                 continue
             placed = False
             while True:
-                if self.cache.can_extend(req.request_id, n):
-                    self.cache.extend(req.request_id, n)
+                if self.cache.try_extend(req.request_id, n):
                     placed = True
                     break
                 if self.running[-1] is not req:
