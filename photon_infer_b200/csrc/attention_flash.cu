@@ -63,6 +63,11 @@ __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float fast_exp2(float x) {       // 2^x; -inf gives 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -110,7 +115,9 @@ __device__ __forceinline__ void load_kv_tile(const FlashParams& P, const int* ta
 // One warp: scores of its 16 rows against NT*8 keys starting at key row `krow` of the K tile, running
 // softmax, weighted sum with the same keys of the V tile.  qa: the rows' A fragments.  pos0/pos1 and
 // lo0/lo1: last and first visible key of the lane's two rows (row lane/4 and lane/4 + 8).
-template <int NT>
+// MASK false: every key of the tile is visible to every row of the warp (the caller has checked), so
+// the comparisons are left out.
+template <int NT, bool MASK>
 __device__ __forceinline__ void warp_tile(const uint32_t (&qa)[FA_KD][4], const bf16* ks, const bf16* vs, int krow,
                                           int key_base, int pos0, int pos1, int lo0, int lo1, float scale_log2,
                                           float (&m)[2], float (&l)[2], float (&o)[FA_ND][4]) {
@@ -131,16 +138,18 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qa)[FA_KD][4], const 
       mma_bf16(s[j + 1], qa[kd], b[2], b[3]);
     }
   }
-  // scale, mask, running softmax (base 2)
+  // scale, mask, running softmax (base 2); the scale is applied inside the exponent: 2^(s*c - m*c)
   const int c2 = (lane & 3) * 2;
   float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
   for (int j = 0; j < NT; ++j) {
-    const int key = key_base + krow + j * 8 + c2;
-    s[j][0] = (key >= lo0 && key <= pos0) ? s[j][0] * scale_log2 : -INFINITY;
-    s[j][1] = (key + 1 >= lo0 && key + 1 <= pos0) ? s[j][1] * scale_log2 : -INFINITY;
-    s[j][2] = (key >= lo1 && key <= pos1) ? s[j][2] * scale_log2 : -INFINITY;
-    s[j][3] = (key + 1 >= lo1 && key + 1 <= pos1) ? s[j][3] * scale_log2 : -INFINITY;
+    if (MASK) {
+      const int key = key_base + krow + j * 8 + c2;
+      s[j][0] = (key >= lo0 && key <= pos0) ? s[j][0] : -INFINITY;
+      s[j][1] = (key + 1 >= lo0 && key + 1 <= pos0) ? s[j][1] : -INFINITY;
+      s[j][2] = (key >= lo1 && key <= pos1) ? s[j][2] : -INFINITY;
+      s[j][3] = (key + 1 >= lo1 && key + 1 <= pos1) ? s[j][3] : -INFINITY;
+    }
     mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
     mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
   }
@@ -148,17 +157,18 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qa)[FA_KD][4], const 
   mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
   mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
   mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-  const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+  // m holds the running maximum of the scaled scores (scale_log2 > 0, so the order is kept)
+  const float mn0 = fmaxf(m[0], mx0 * scale_log2), mn1 = fmaxf(m[1], mx1 * scale_log2);
   const float sub0 = (mn0 == -INFINITY) ? 0.f : mn0, sub1 = (mn1 == -INFINITY) ? 0.f : mn1;
-  const float corr0 = (m[0] == -INFINITY) ? 0.f : exp2f(m[0] - sub0);
-  const float corr1 = (m[1] == -INFINITY) ? 0.f : exp2f(m[1] - sub1);
+  const float corr0 = fast_exp2(m[0] - sub0);             // 2^(-inf) = 0 for the first tile
+  const float corr1 = fast_exp2(m[1] - sub1);
   m[0] = mn0; m[1] = mn1;
   float sum0 = 0.f, sum1 = 0.f;
   uint32_t pa[NT / 2][4];
 #pragma unroll
   for (int j = 0; j < NT; ++j) {
-    const float p0 = exp2f(s[j][0] - sub0), p1 = exp2f(s[j][1] - sub0);
-    const float p2 = exp2f(s[j][2] - sub1), p3 = exp2f(s[j][3] - sub1);
+    const float p0 = fast_exp2(fmaf(s[j][0], scale_log2, -sub0)), p1 = fast_exp2(fmaf(s[j][1], scale_log2, -sub0));
+    const float p2 = fast_exp2(fmaf(s[j][2], scale_log2, -sub1)), p3 = fast_exp2(fmaf(s[j][3], scale_log2, -sub1));
     sum0 += p0 + p1; sum1 += p2 + p3;
     pa[j >> 1][(j & 1) * 2] = pack_bf16(p0, p1);
     pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
@@ -253,8 +263,14 @@ flash_attention_kernel(const FlashParams P) {
     }
   }
   int warp_pos_max = max(pos_r[0], pos_r[1]);
+  int warp_pos_min = min(pos_r[0], pos_r[1]);             // -1 when the warp has a row beyond the request's rows
+  int warp_lo_max = max(lo_r[0], lo_r[1]);
 #pragma unroll
-  for (int o2 = 16; o2 > 0; o2 >>= 1) warp_pos_max = max(warp_pos_max, __shfl_xor_sync(0xffffffffu, warp_pos_max, o2));
+  for (int o2 = 16; o2 > 0; o2 >>= 1) {
+    warp_pos_max = max(warp_pos_max, __shfl_xor_sync(0xffffffffu, warp_pos_max, o2));
+    warp_pos_min = min(warp_pos_min, __shfl_xor_sync(0xffffffffu, warp_pos_min, o2));
+    warp_lo_max = max(warp_lo_max, __shfl_xor_sync(0xffffffffu, warp_lo_max, o2));
+  }
 
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   float o[FA_ND][4];
@@ -282,13 +298,24 @@ flash_attention_kernel(const FlashParams P) {
     const int key_base = (tile_begin + i) * FA_TILE_K;
     if (KEYS_MODE) {
       // every warp takes 16 keys of the tile
-      if (key_base + warp * 16 <= warp_pos_max)
-        warp_tile<2>(qa, stage_k(st), stage_v(st), warp * 16, key_base, pos_r[0], pos_r[1], lo_r[0], lo_r[1],
-                     P.scale_log2, m, l, o);
+      const int k0 = key_base + warp * 16;
+      if (k0 <= warp_pos_max) {
+        if (k0 + 15 <= warp_pos_min && k0 >= warp_lo_max)
+          warp_tile<2, false>(qa, stage_k(st), stage_v(st), warp * 16, key_base, pos_r[0], pos_r[1], lo_r[0], lo_r[1],
+                              P.scale_log2, m, l, o);
+        else
+          warp_tile<2, true>(qa, stage_k(st), stage_v(st), warp * 16, key_base, pos_r[0], pos_r[1], lo_r[0], lo_r[1],
+                             P.scale_log2, m, l, o);
+      }
     } else {
-      if (key_base <= warp_pos_max)                                        // tiles after the warp's last row are skipped
-        warp_tile<8>(qa, stage_k(st), stage_v(st), 0, key_base, pos_r[0], pos_r[1], lo_r[0], lo_r[1],
-                     P.scale_log2, m, l, o);
+      if (key_base <= warp_pos_max) {                                      // tiles after the warp's last row are skipped
+        if (key_base + FA_TILE_K - 1 <= warp_pos_min && key_base >= warp_lo_max)
+          warp_tile<8, false>(qa, stage_k(st), stage_v(st), 0, key_base, pos_r[0], pos_r[1], lo_r[0], lo_r[1],
+                              P.scale_log2, m, l, o);
+        else
+          warp_tile<8, true>(qa, stage_k(st), stage_v(st), 0, key_base, pos_r[0], pos_r[1], lo_r[0], lo_r[1],
+                             P.scale_log2, m, l, o);
+      }
     }
     __syncthreads();                                                       // the stage may be overwritten
   }
@@ -401,7 +428,7 @@ PHOTON_API int photon_flash_attention(const void* q, long q_stride, void* out, l
                                       int page_size, int num_pages, int window, float scale, int num_splits,
                                       int mode, int* err, cudaStream_t stream) {
   if (S <= 0) return 0;
-  if (d != HEAD_DIM || n_kv <= 0 || n_q % n_kv) return PHOTON_ERR_UNSUPPORTED;
+  if (d != HEAD_DIM || n_kv <= 0 || n_q % n_kv || !(scale > 0.f)) return PHOTON_ERR_UNSUPPORTED;
   if (((uintptr_t)q % 16) || ((size_t)q_stride * 2) % 16 || ((uintptr_t)k_cache % 16) || ((uintptr_t)v_cache % 16))
     return PHOTON_ERR_ARGUMENT;
   if (num_splits < 1 || num_splits > 65535 || n_kv > 65535) return PHOTON_ERR_UNSUPPORTED;
