@@ -122,8 +122,8 @@ class PagedAttention(Mixer):
                             self.n_q, self.n_kv, self.head_dim, self.window, self.scale, ctx.error_flag)
 
 
-def choose_splits(blocks_without_split: int, max_keys: int, round_keys: int, target_blocks: int = 370) -> int:
-    """Shares of keys per token: about as many blocks as are resident at once on 148 SMs (one wave), no share below one round."""
+def choose_splits(blocks_without_split: int, max_keys: int, round_keys: int, target_blocks: int = 256) -> int:
+    """Shares of keys per token: about 256 blocks (measured best on 148 SMs: more shares cost more in the merge than they gain), no share below one round."""
     by_fill = -(-target_blocks // max(blocks_without_split, 1))
     by_keys = -(-max(max_keys, 1) // round_keys)
     return max(1, min(by_fill, by_keys, 64))
