@@ -70,7 +70,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -134,7 +134,6 @@ def main() -> int:
     from photon_infer_b200.engine.loading import build_runner
     from photon_infer_b200.engine.runner import StepEntry
     from photon_infer_b200.kernels import ops
-    from photon_infer_b200.sampling import Sampler
     from photon_infer_b200.weights import write_random_model
 
     hbm_peak, tf_peak, peak_src = peaks()
@@ -155,7 +154,6 @@ def main() -> int:
         runner = build_runner(folder, options)
     model, cache = runner.model, runner.cache
     vocab = cfg["vocab_size"]
-    sampler = Sampler(runner.device)
     gen = torch.Generator().manual_seed(1)
 
     def rand_ids(n):
@@ -173,9 +171,9 @@ def main() -> int:
         """Device-timed decode steps: tokens in, logits, sampled ids on the device."""
         fill(batch)
         ids = [rand_ids(batch) for _ in range(steps + warmup)]
+        greedy = ([0.0] * batch, [0.0] * batch)
         def one(k):
-            res = runner.step([StepEntry(("d", i), [ids[k][i]], [0]) for i in range(batch)])
-            return sampler.sample(res.logits, [0.0] * batch, [0.0] * batch)
+            return runner.step([StepEntry(("d", i), [ids[k][i]], [0]) for i in range(batch)], sampling=greedy).tokens
         for k in range(warmup):
             one(k)
         torch.cuda.synchronize()

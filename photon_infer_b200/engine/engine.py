@@ -85,13 +85,13 @@ class ContinuousBatchEngine:
             entries.append(StepEntry(it.request.request_id, tokens, [it.num_tokens - 1] if it.samples else []))
             if it.samples:
                 samplers.append(it.request)
-        result = self.runner.step(entries, pages_taken=True)
+        temps = [r.params.temperature for r in samplers]
+        us = [uniform(r.params.seed, r.request_id, r.num_generated()) if r.params.temperature > 0 else 0.0
+              for r in samplers]
+        result = self.runner.step(entries, pages_taken=True, sampling=(temps, us) if samplers else None)
         sampled: Dict[int, int] = {}
         if samplers:
-            temps = [r.params.temperature for r in samplers]
-            us = [uniform(r.params.seed, r.request_id, r.num_generated()) if r.params.temperature > 0 else 0.0
-                  for r in samplers]
-            ids = self.sampler.sample(result.logits, temps, us)
+            ids = result.tokens
             n = len(samplers)
             if self._host_tokens is None or self._host_tokens.numel() < n:
                 self._host_tokens = torch.empty(max(n, 256), dtype=torch.int32, pin_memory=True)

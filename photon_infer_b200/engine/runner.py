@@ -32,6 +32,7 @@ class StepEntry:
 class StepResult:
     logits: torch.Tensor                # float32 [n_wanted, vocab] on the device
     rows: List[tuple]                   # (request_id, position in the request) of each row
+    tokens: Optional[torch.Tensor] = None   # int32 [n_wanted]: sampled ids, when sampling was asked for
 
 
 @dataclasses.dataclass
@@ -40,6 +41,7 @@ class _DecodeGraph:
     static_input: torch.Tensor
     logits: torch.Tensor
     kernels: int                        # kernels of this package inside one replay
+    tokens: Optional[torch.Tensor] = None
 
 
 _DEVICE_ERRORS = {1: "token id {1} at token {0} of the step is outside the vocabulary of {2}",
@@ -77,8 +79,11 @@ class ModelRunner:
         return self._pinned
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry], pages_taken: bool = False) -> StepResult:
-        """``pages_taken``: the caller (the scheduler) has already taken the pages these tokens need."""
+    def step(self, entries: Sequence[StepEntry], pages_taken: bool = False,
+             sampling: Optional[tuple] = None) -> StepResult:
+        """``pages_taken``: the caller (the scheduler) has already taken the pages these tokens need.
+        ``sampling``: (temperatures, uniform numbers), one of each per wanted row in order; the step then
+        also samples on the device (inside the captured graph for decode steps) and returns the ids."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return StepResult(torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device), [])
@@ -113,19 +118,31 @@ class ModelRunner:
         for e in entries_to_extend:
             cache.extend(e.request_id, len(e.tokens))
 
+        tokens = None
         if self.use_cuda_graphs and len(entries) <= self.max_graph_batch and all(len(e.tokens) == 1 for e in entries):
-            logits, ctx, rows = self._graph_step(entries)
+            logits, ctx, rows, tokens = self._graph_step(entries, sampling)
         else:
-            ctx, logit_rows, rows = self._build_context(entries)
+            ctx, logit_rows, rows = self._build_context(entries, sampling=sampling)
             logits = self.model.forward(ctx, self._layer_caches, logit_rows)
+            if sampling is not None:
+                tokens = self._sample(logits)
         for e in entries:
             cache.commit(e.request_id, len(e.tokens))
         self.steps += 1
         self.tokens += ctx.num_tokens
-        return StepResult(logits, rows)
+        return StepResult(logits, rows, tokens)
+
+    def _sample(self, logits: torch.Tensor) -> torch.Tensor:
+        """Samples every row of ``logits`` with the temperatures and uniform numbers of the last built step."""
+        from ..kernels import ops
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
+        if logits.shape[0]:
+            ops.sample(logits, self._temps, self._uniforms, out)
+        return out
 
     def _build_context(self, entries: Sequence[StepEntry], widths: Optional[List[int]] = None,
-                       static_input: Optional[torch.Tensor] = None, bound_context: Optional[int] = None):
+                       static_input: Optional[torch.Tensor] = None, bound_context: Optional[int] = None,
+                       sampling: Optional[tuple] = None):
         """Builds every index array of the step in one pinned buffer and copies it to the device once.
         ``widths``: block-table widths to use (default: what the requests need).  ``static_input``: a
         device buffer of the same layout to copy into (for a captured graph).  ``bound_context``: the
@@ -141,7 +158,8 @@ class ModelRunner:
             widths = cache.table_width(rids)
         G = len(cache.groups)
         # layout of the one staging buffer (int32 counts)
-        sizes = [T, T, T, S + 1, S, S, n_want] + [T] * G + [S * w for w in widths]
+        n_samp = n_want if sampling is not None else 0
+        sizes = [T, T, T, S + 1, S, S, n_want] + [T] * G + [S * w for w in widths] + [n_samp, n_samp]
         offs = np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])]).astype(np.int64)
         total = int(offs[-1])
         self._last_total = total
@@ -195,6 +213,9 @@ class ModelRunner:
                     cache.fill_slot_mapping(g, e.request_id, starts[s], q_lens[s], sm[t:t + q_lens[s]])
                     t += q_lens[s]
                 cache.fill_block_table(g, rids, seg(7 + G + g).reshape(S, widths[g]))
+        if sampling is not None and n_samp:
+            seg(7 + 2 * G).view(np.float32)[:] = sampling[0]
+            seg(8 + 2 * G).view(np.float32)[:] = sampling[1]
         if static_input is not None:
             dev = static_input
             dev[:total].copy_(stage[:total], non_blocking=True)
@@ -212,13 +233,16 @@ class ModelRunner:
             host_query_lens=q_lens, host_context_lens=[a + b for a, b in zip(starts, q_lens)],
             host_start_positions=starts, max_query_len=max(q_lens),
             max_context_len=bound_context or max(a + b for a, b in zip(starts, q_lens)), error_flag=self.error_flag)
+        if sampling is not None:
+            self._temps = dseg(7 + 2 * G).view(torch.float32)
+            self._uniforms = dseg(8 + 2 * G).view(torch.float32)
         # the staging buffer is reused by the next step, which waits for this copy first
         self._copy_done = torch.cuda.Event()
         self._copy_done.record()
         return ctx, dseg(6), rows
 
     # ------------------------------------------------------------------ decode steps as CUDA graphs
-    def _graph_step(self, entries: Sequence[StepEntry]):
+    def _graph_step(self, entries: Sequence[StepEntry], sampling: Optional[tuple] = None):
         """A step of single tokens replays a captured graph: same kernels, one launch.  A graph is
         captured per (batch size, block-table width, wanted rows); the width is a power of two of
         pages, so a graph serves until a request outgrows it.  The logits it returns live in the
@@ -232,26 +256,29 @@ class ModelRunner:
                 b *= 2
             widths.append(b)
         n_want = sum(len(e.want) for e in entries)
-        key = (len(entries), tuple(widths), n_want)
+        key = (len(entries), tuple(widths), n_want, sampling is not None)
         bound = max(w * g.page_size for w, g in zip(widths, cache.groups)) if widths else 1
         graph = self._graphs.get(key)
         if graph is None:
-            graph = self._capture(entries, widths, bound)
+            graph = self._capture(entries, widths, bound, sampling)
             self._graphs[key] = graph
-        ctx, _, rows = self._build_context(entries, widths, graph.static_input, bound)
+        ctx, _, rows = self._build_context(entries, widths, graph.static_input, bound, sampling)
         graph.graph.replay()
         self.graph_kernel_launches += graph.kernels
-        return graph.logits, ctx, rows
+        return graph.logits, ctx, rows, graph.tokens
 
-    def _capture(self, entries: Sequence[StepEntry], widths: List[int], bound: int) -> "_DecodeGraph":
+    def _capture(self, entries: Sequence[StepEntry], widths: List[int], bound: int,
+                 sampling: Optional[tuple] = None) -> "_DecodeGraph":
         from ..kernels import ops
         # the layout depends only on (batch, widths, wanted rows): one build gives the buffer's size
-        self._build_context(entries, widths, None, bound)
+        self._build_context(entries, widths, None, bound, sampling)
         size = self._last_total
         static_input = torch.zeros(size, dtype=torch.int32, device=self.device)
-        ctx, logit_rows, _ = self._build_context(entries, widths, static_input, bound)
+        ctx, logit_rows, _ = self._build_context(entries, widths, static_input, bound, sampling)
         # once outside the capture: modules load, cuBLAS makes its workspace
-        self.model.forward(ctx, self._layer_caches, logit_rows)
+        warm = self.model.forward(ctx, self._layer_caches, logit_rows)
+        if sampling is not None:
+            self._sample(warm)
         torch.cuda.synchronize()
         if self._graph_pool is None:
             self._graph_pool = torch.cuda.graph_pool_handle()
@@ -259,8 +286,9 @@ class ModelRunner:
         before = ops.launch_count()
         with torch.cuda.graph(g, pool=self._graph_pool):
             logits = self.model.forward(ctx, self._layer_caches, logit_rows)
+            tokens = self._sample(logits) if sampling is not None else None
         kernels = ops.launch_count() - before
-        return _DecodeGraph(g, static_input, logits, kernels)
+        return _DecodeGraph(g, static_input, logits, kernels, tokens)
 
     # ------------------------------------------------------------------ errors from the device
     def check_device_errors(self) -> None:
