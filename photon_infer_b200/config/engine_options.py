@@ -31,6 +31,7 @@ class EngineOptions:
     max_model_len: Optional[int] = None     # longest request; None: max_position_embeddings
     seed: int = 0
     use_cuda_graphs: bool = True
+    async_decode: bool = True               # enqueue the next decode step before reading the last one's ids
     device: str = "cuda:0"
 
     def validate(self) -> None:

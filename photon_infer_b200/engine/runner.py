@@ -80,10 +80,12 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence[StepEntry], pages_taken: bool = False,
-             sampling: Optional[tuple] = None) -> StepResult:
+             sampling: Optional[tuple] = None, device_tokens: Optional[torch.Tensor] = None) -> StepResult:
         """``pages_taken``: the caller (the scheduler) has already taken the pages these tokens need.
         ``sampling``: (temperatures, uniform numbers), one of each per wanted row in order; the step then
-        also samples on the device (inside the captured graph for decode steps) and returns the ids."""
+        also samples on the device (inside the captured graph for decode steps) and returns the ids.
+        ``device_tokens``: int32 ids on the device, one per entry, that replace the entries' (single) tokens;
+        a decode step can then be enqueued before the host has seen the ids the previous step sampled."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return StepResult(torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device), [])
@@ -119,10 +121,14 @@ class ModelRunner:
             cache.extend(e.request_id, len(e.tokens))
 
         tokens = None
+        if device_tokens is not None and not all(len(e.tokens) == 1 for e in entries):
+            raise PhotonError(ErrorCode.INVALID_ARGUMENT, "device_tokens needs entries of one token each")
         if self.use_cuda_graphs and len(entries) <= self.max_graph_batch and all(len(e.tokens) == 1 for e in entries):
-            logits, ctx, rows, tokens = self._graph_step(entries, sampling)
+            logits, ctx, rows, tokens = self._graph_step(entries, sampling, device_tokens)
         else:
             ctx, logit_rows, rows = self._build_context(entries, sampling=sampling)
+            if device_tokens is not None:
+                ctx.token_ids.copy_(device_tokens[: ctx.num_tokens])
             logits = self.model.forward(ctx, self._layer_caches, logit_rows)
             if sampling is not None:
                 tokens = self._sample(logits)
@@ -242,7 +248,8 @@ class ModelRunner:
         return ctx, dseg(6), rows
 
     # ------------------------------------------------------------------ decode steps as CUDA graphs
-    def _graph_step(self, entries: Sequence[StepEntry], sampling: Optional[tuple] = None):
+    def _graph_step(self, entries: Sequence[StepEntry], sampling: Optional[tuple] = None,
+                    device_tokens: Optional[torch.Tensor] = None):
         """A step of single tokens replays a captured graph: same kernels, one launch.  A graph is
         captured per (batch size, block-table width, wanted rows); the width is a power of two of
         pages, so a graph serves until a request outgrows it.  The logits it returns live in the
@@ -263,6 +270,8 @@ class ModelRunner:
             graph = self._capture(entries, widths, bound, sampling)
             self._graphs[key] = graph
         ctx, _, rows = self._build_context(entries, widths, graph.static_input, bound, sampling)
+        if device_tokens is not None:
+            ctx.token_ids.copy_(device_tokens[: ctx.num_tokens])      # a view of the graph's input buffer
         graph.graph.replay()
         self.graph_kernel_launches += graph.kernels
         return graph.logits, ctx, rows, graph.tokens

@@ -209,13 +209,26 @@ class ContinuousBatchScheduler:
                     self._prefill += it.num_tokens
         return batch
 
+    def continue_decode(self, requests: Sequence[InferenceRequest]) -> ScheduledBatch:
+        """The batch that feeds each of these RUNNING requests its next token, for a caller that enqueues
+        the step before the previous step's tokens have reached the host (pages already taken)."""
+        batch = ScheduledBatch([ScheduledItem(r, 1, True) for r in requests])
+        self._steps += 1
+        self._tokens += len(batch.items)
+        self._decode += len(batch.items)
+        return batch
+
     # ------------------------------------------------------------------ after the step
-    def update_after_step(self, batch: ScheduledBatch, sampled: Dict[int, int]) -> List[InferenceRequest]:
+    def update_after_step(self, batch: ScheduledBatch, sampled: Dict[int, int],
+                          skip: Sequence[int] = ()) -> List[InferenceRequest]:
         """``sampled`` maps request ids to the token sampled after their portion (present for every
-        item whose ``samples`` is true).  Returns the requests that finished."""
+        item whose ``samples`` is true).  ``skip``: requests that finished while this step was in flight;
+        their items are ignored.  Returns the requests that finished."""
         finished = []
         for it in batch.items:
             req = it.request
+            if req.request_id in skip:
+                continue
             if self.commits_lengths:
                 self.cache.commit(req.request_id, it.num_tokens)
             req.add_computed_tokens(it.num_tokens)

@@ -211,3 +211,42 @@ def test_command_line(folders):
     assert bad.returncode != 0 and "CUDA only" in bad.stderr
     bad = subprocess.run(cmd + ["--quantize"], capture_output=True, text=True, timeout=120)
     assert bad.returncode != 0 and "INT8" in bad.stderr
+
+
+def test_pipelined_decode_equals_step_by_step(folders):
+    """Decode steps enqueued one ahead (ids still on the device) give the same tokens and finish reasons as
+    steps that wait for their ids, also when one request meets end-of-sequence while the next step is
+    already in flight, when another runs out of new tokens, and with temperature sampling."""
+    import json
+    from photon_infer_b200 import ContinuousBatchEngine
+    from plain.llama_plain import PlainLlama
+    name = "tiny_a"
+    m = PlainLlama.from_folder(folders[name])
+    prompts = [random_ids(n, 256, seed=70 + n) for n in (12, 7, 21, 15)]
+    free_run = m.greedy(prompts[0], 30)
+    eos = free_run[9]                                       # request 0 stops at its first occurrence of this id
+    cfg = json.load(open(os.path.join(folders[name], "config.json")))
+    cfg["eos_token_id"] = eos
+    alt = folders[name] + "_eos2"
+    os.makedirs(alt, exist_ok=True)
+    json.dump(cfg, open(os.path.join(alt, "config.json"), "w"))
+    if not os.path.exists(os.path.join(alt, "model.safetensors")):
+        os.link(os.path.join(folders[name], "model.safetensors"), os.path.join(alt, "model.safetensors"))
+
+    def run(async_decode):
+        eng = ContinuousBatchEngine(alt, _options(name, "float32", async_decode=async_decode))
+        ids = [eng.add_request(prompts[0], max_new_tokens=30),
+               eng.add_request(prompts[1], max_new_tokens=5, ignore_eos=True),
+               eng.add_request(prompts[2], max_new_tokens=40, temperature=0.9, seed=5, ignore_eos=True),
+               eng.add_request(prompts[3], max_new_tokens=33, ignore_eos=True)]
+        out = eng.run_until_complete()
+        assert eng.runner.cache.free_pages() == [g.num_pages for g in eng.runner.cache.groups]
+        return [(out[i], eng.result(i).finish_reason) for i in ids], eng
+
+    a, eng_a = run(True)
+    b, _ = run(False)
+    assert a == b
+    assert a[0][1] == "eos" and a[0][0] == free_run[: free_run.index(eos) + 1]
+    assert a[1][1] == "length" and len(a[1][0]) == 5
+    assert a[3][0] == m.greedy(prompts[3], 33)
+    assert eng_a._inflight is None
