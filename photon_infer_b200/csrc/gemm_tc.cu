@@ -26,9 +26,13 @@
 #include <cuda.h>
 
 #define TC_BM 128
+#ifndef TC_BN
 #define TC_BN 256
+#endif
 #define TC_BK 64                      // 64 bf16 = 128 bytes = one swizzle row
+#ifndef TC_STAGES
 #define TC_STAGES 4
+#endif
 #define TC_UMMA_K 16
 #define TC_THREADS 192                // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
 #define TC_WAIT_LIMIT (1u << 20)
