@@ -38,6 +38,7 @@ class PagedAttention(Mixer):
         self.position_encoding = position_encoding
         self.w_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
+        self.pairs_adjacent = False             # set at load: the convention the rotation kernel runs in
 
     def required_kernels(self, dtype):
         mods = list(self.kernel_modules)
@@ -56,8 +57,20 @@ class PagedAttention(Mixer):
                 TensorSpec("o_proj.weight", (H, self.n_q * d))]
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.w_qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"],
-                                tensors["v_proj.weight"]], dim=0).contiguous()
+        wq, wk = tensors["q_proj.weight"], tensors["k_proj.weight"]
+        pe = self.position_encoding
+        self.pairs_adjacent = bool(getattr(pe, "interleaved", False))
+        if isinstance(pe, RotaryEncoding) and not pe.interleaved:
+            # Files in the half-split convention pair feature j with j + d/2.  The rows of the q and k
+            # projections are reordered inside every head to [0, d/2, 1, d/2 + 1, ...], which makes the
+            # partners neighbours (the same rotation then runs in the neighbour convention) and leaves
+            # every score q.k unchanged, because q and k are permuted alike.  Values are untouched.
+            d = self.head_dim
+            order = torch.stack([torch.arange(d // 2), torch.arange(d // 2) + d // 2], dim=1).reshape(-1)
+            wq = wq.view(self.n_q, d, -1)[:, order.to(wq.device), :].reshape(self.n_q * d, -1)
+            wk = wk.view(self.n_kv, d, -1)[:, order.to(wk.device), :].reshape(self.n_kv * d, -1)
+            self.pairs_adjacent = True
+        self.w_qkv = torch.cat([wq, wk, tensors["v_proj.weight"]], dim=0).contiguous()
         self.w_o = tensors["o_proj.weight"].contiguous()
 
     def weight_bytes(self) -> int:
@@ -85,7 +98,7 @@ class PagedAttention(Mixer):
         if isinstance(pe, RotaryEncoding):
             # rotation and cache write in one pass over the row
             ops.rope_kv_write(q, k, v, ctx.positions,
-                              pe.inv_freq, pe.interleaved, group.slot_mapping, k_cache, v_cache,
+                              pe.inv_freq, self.pairs_adjacent, group.slot_mapping, k_cache, v_cache,
                               self.n_q, self.n_kv, d, ctx.error_flag)
         else:
             if pe is not None:
