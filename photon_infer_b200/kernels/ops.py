@@ -322,6 +322,68 @@ def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilog
              _ptr(scratch), scratch.numel(), _ptr(tickets), tickets.numel(), _stream()), "skinny_gemm")
 
 
+def skinny_fused_supported(residual: torch.Tensor, weight: torch.Tensor) -> bool:
+    """The decode-step product with the residual add and the norm folded in: up to 8 rows of a contiguous
+    float32 residual stream, bfloat16 weights, K a multiple of 8."""
+    M, K = residual.shape
+    return (residual.dtype == torch.float32 and residual.is_contiguous() and weight.dtype == torch.bfloat16
+            and weight.is_contiguous() and 1 <= M <= 8 and K % 8 == 0 and weight.shape[1] == K
+            and weight.data_ptr() % 16 == 0 and residual.data_ptr() % 16 == 0)
+
+
+def skinny_fused(residual: torch.Tensor, delta: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
+                 weight: torch.Tensor, epilogue: str, rope: Optional[dict] = None,
+                 err: Optional[torch.Tensor] = None):
+    """``x = residual + delta``; ``out = epilogue(rmsnorm(x; norm_weight, eps) @ weight^T)`` in one kernel.
+    Returns ``(out, new_residual)``; the input residual is left untouched (the sum goes to a new tensor).
+    ``epilogue``: ``"bf16"``, ``"swiglu"`` (``weight`` = gate rows then up rows) or ``"qkv"`` with
+    ``rope = dict(positions, inv_freq, slot_mapping, k_cache, v_cache, n_q, n_kv, head_dim)``: q and k are
+    rotated (partners must be neighbouring rows of ``weight``), q is returned ``[M, n_q * d]`` wide in
+    ``out[:, :n_q * d]``, k and v go into the paged cache."""
+    _cuda(residual, delta, norm_weight, weight, err)
+    M, K = residual.shape
+    N = weight.shape[0]
+    if not skinny_fused_supported(residual, weight):
+        raise PhotonError(ErrorCode.UNSUPPORTED_SIZE, "skinny_fused: needs <= 8 float32 rows, bfloat16 weights, K % 8 == 0")
+    if delta is not None and (delta.shape != residual.shape or delta.dtype != torch.bfloat16 or not delta.is_contiguous()
+                              or delta.data_ptr() % 16):
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "skinny_fused: delta must be contiguous bfloat16 like the residual")
+    if norm_weight.numel() != K or norm_weight.data_ptr() % 16:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "skinny_fused: norm weight must be [K]")
+    code = {"bf16": 0, "swiglu": 2, "qkv": 3}[epilogue]
+    new_residual = torch.empty_like(residual) if delta is not None else residual
+    r = rope or {}
+    if epilogue == "qkv":
+        n_q, n_kv, d = r["n_q"], r["n_kv"], r["head_dim"]
+        if N != (n_q + 2 * n_kv) * d or d % 2:
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, "skinny_fused: weight must hold q, k and v rows")
+        k_cache, v_cache = r["k_cache"], r["v_cache"]
+        if k_cache.dtype != torch.bfloat16 or k_cache.shape != v_cache.shape or k_cache.dim() != 4 \
+                or k_cache.shape[1] != n_kv or k_cache.shape[3] != d or not k_cache.is_contiguous() \
+                or not v_cache.is_contiguous():
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, "skinny_fused: caches must be contiguous bfloat16 [pages, n_kv, page, d]")
+        _int32(r["positions"], "positions")
+        _int32(r["slot_mapping"], "slot_mapping")
+        out = torch.empty((M, n_q * d), dtype=torch.bfloat16, device=residual.device)
+        page_size, num_slots = k_cache.shape[2], k_cache.shape[0] * k_cache.shape[2]
+    else:
+        n_q = n_kv = d = 0
+        k_cache = v_cache = None
+        page_size, num_slots = 1, 0
+        out = torch.empty((M, N // 2 if epilogue == "swiglu" else N), dtype=torch.bfloat16, device=residual.device)
+    if err is None:
+        err = _error_word(residual.device)
+    f = _fn("gemm_skinny_fused", "photon_skinny_fused",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
+             c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_long,
+             c_void_p, c_void_p])
+    _check(f(_ptr(residual), _ptr(new_residual if delta is not None else None), _ptr(delta), _ptr(norm_weight),
+             _dtype_code(norm_weight), float(eps), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K,
+             code, _ptr(r.get("positions")), _ptr(r.get("inv_freq")), _ptr(r.get("slot_mapping")), _ptr(k_cache),
+             _ptr(v_cache), n_q, n_kv, d, page_size, num_slots, _ptr(err), _stream()), "skinny_fused")
+    return out, new_residual
+
+
 def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     """``silu(x Wg^T) * (x Wu^T)`` with ``w_gate_up = [Wg; Wu]``: one kernel for few rows, else the
     product followed by the SwiGLU kernel."""

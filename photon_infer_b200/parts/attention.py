@@ -43,7 +43,7 @@ class PagedAttention(Mixer):
     def required_kernels(self, dtype):
         mods = list(self.kernel_modules)
         if dtype == torch.bfloat16:
-            mods.extend(["gemm_skinny", "gemm_tc"])
+            mods.extend(["gemm_skinny", "gemm_skinny_fused", "gemm_tc"])
         if ops.flash_attention_supported(dtype, self.head_dim):
             mods.append(("attention_flash", {"HEAD_DIM": self.head_dim}))
         return mods
@@ -78,6 +78,25 @@ class PagedAttention(Mixer):
 
     def cache_spec(self) -> Optional[PagedCacheSpec]:
         return PagedCacheSpec(self.n_kv, self.head_dim, self.window)
+
+    # -- decode steps: residual sum, norm, q/k/v products, rotation and cache write in one kernel
+    def fuses_norm(self, norm, residual, ctx, cache) -> bool:
+        from .norm import RMSNorm
+        return (isinstance(norm, RMSNorm) and ctx.dtype == torch.bfloat16 and not cache.shared
+                and isinstance(self.position_encoding, RotaryEncoding) and self.pairs_adjacent
+                and cache.k is not None and ops.skinny_fused_supported(residual, self.w_qkv))
+
+    def forward_with_norm(self, residual, delta, norm, ctx, cache):
+        group = ctx.groups[cache.group]
+        pe = self.position_encoding
+        q, residual = ops.skinny_fused(
+            residual, delta, norm.weight, norm.eps, self.w_qkv, "qkv",
+            rope=dict(positions=ctx.positions, inv_freq=pe.inv_freq, slot_mapping=group.slot_mapping, k_cache=cache.k,
+                      v_cache=cache.v, n_q=self.n_q, n_kv=self.n_kv, head_dim=self.head_dim),
+            err=ctx.error_flag)
+        attn = torch.empty((q.shape[0], self.n_q * self.head_dim), dtype=q.dtype, device=q.device)
+        self.attend(q, attn, ctx, cache)
+        return project(attn, self.w_o), residual
 
     # -- one step
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:

@@ -164,9 +164,26 @@ class Mixer(Part):
         """``h [T, H]`` normed input in the run dtype; returns ``[T, H]`` to add to the residual."""
         raise NotImplementedError
 
+    # Optional fast path.  A mixer that can take the residual sum and the norm into its first kernel
+    # answers True and implements forward_with_norm; the block then skips the separate norm pass.
+    def fuses_norm(self, norm: Norm, residual: torch.Tensor, ctx: StepContext, cache: LayerCache) -> bool:
+        return False
+
+    def forward_with_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor], norm: Norm,
+                          ctx: StepContext, cache: LayerCache) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Returns ``(output, new residual)`` where the new residual is ``residual + delta``."""
+        raise NotImplementedError
+
 
 class FeedForward(Part):
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+    def fuses_norm(self, norm: Norm, residual: torch.Tensor, ctx: StepContext) -> bool:
+        return False
+
+    def forward_with_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor], norm: Norm,
+                          ctx: StepContext) -> Tuple[torch.Tensor, torch.Tensor]:
         raise NotImplementedError
 
 

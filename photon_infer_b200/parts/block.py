@@ -23,10 +23,18 @@ class PreNormBlock(Block):
 
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], ctx: StepContext,
                 cache: LayerCache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
-        h = self.norm1.add_forward(delta, residual, ctx.dtype)
-        a = self._mixer.forward(h, ctx, cache)
-        h2 = self.norm2.add_forward(a, residual, ctx.dtype)
-        return residual, self.feed_forward.forward(h2, ctx)
+        # a part may take the residual sum and the norm into its first kernel (decode steps)
+        if self._mixer.fuses_norm(self.norm1, residual, ctx, cache):
+            a, residual = self._mixer.forward_with_norm(residual, delta, self.norm1, ctx, cache)
+        else:
+            h = self.norm1.add_forward(delta, residual, ctx.dtype)
+            a = self._mixer.forward(h, ctx, cache)
+        if self.feed_forward.fuses_norm(self.norm2, residual, ctx):
+            d, residual = self.feed_forward.forward_with_norm(residual, a, self.norm2, ctx)
+        else:
+            h2 = self.norm2.add_forward(a, residual, ctx.dtype)
+            d = self.feed_forward.forward(h2, ctx)
+        return residual, d
 
 
 register_block("pre_norm", PreNormBlock)

@@ -17,7 +17,7 @@ class SwiGLUFeedForward(FeedForward):
     kernel_modules = ("elementwise",)
 
     def required_kernels(self, dtype):
-        return ["elementwise"] + (["gemm_skinny", "gemm_tc"] if dtype == torch.bfloat16 else [])
+        return ["elementwise"] + (["gemm_skinny", "gemm_skinny_fused", "gemm_tc"] if dtype == torch.bfloat16 else [])
 
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden_size = hidden_size
@@ -36,6 +36,22 @@ class SwiGLUFeedForward(FeedForward):
 
     def weight_bytes(self) -> int:
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
+
+    #: Taking the norm into the gate/up kernel is implemented but off: at the Llama 3.2 1B shape it measured
+    #: 18.9 us against 15.4 us for norm kernel + product, because every one of the 512 blocks re-reads the
+    #: 8 x 2048 residual rows (the product itself is bound by streaming its 67 MB of weights).
+    fuse_norm = False
+
+    def fuses_norm(self, norm, residual, ctx) -> bool:
+        from .norm import RMSNorm
+        return (self.fuse_norm and isinstance(norm, RMSNorm) and ctx is not None and ctx.dtype == torch.bfloat16
+                and ops.skinny_fused_supported(residual, self.w_gate_up))
+
+    def forward_with_norm(self, residual, delta, norm, ctx):
+        """Residual sum, RMSNorm, gate/up products and SwiGLU in one kernel; then the down product."""
+        act, residual = ops.skinny_fused(residual, delta, norm.weight, norm.eps, self.w_gate_up, "swiglu",
+                                         err=ctx.error_flag)
+        return project(act, self.w_down), residual
 
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         act = ops.linear_swiglu(h, self.w_gate_up)

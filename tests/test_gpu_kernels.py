@@ -521,3 +521,67 @@ def test_gemm_tcgen05_swiglu(M, I, K):
     ops.gemm_tc(x, w, out, "swiglu", err)
     assert err.cpu().tolist()[0] == 0
     _close(out, want, torch.bfloat16)
+
+
+@pytest.mark.parametrize("M", [1, 5, 8])
+@pytest.mark.parametrize("K,N", [(64, 48), (120, 400), (2048, 512)])
+@pytest.mark.parametrize("w_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("with_delta", [True, False])
+def test_skinny_fused_norm_product(M, K, N, w_dtype, with_delta):
+    """Residual sum + RMSNorm + product in one kernel, plain and SwiGLU epilogues."""
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(17)
+    res = torch.randn(M, K)
+    delta = torch.randn(M, K).bfloat16() if with_delta else None
+    nw = (1 + 0.1 * torch.randn(K)).to(w_dtype)
+    w = (torch.randn(N, K) / math.sqrt(K)).bfloat16()
+    x = res.double() + (delta.double() if with_delta else 0)
+    h = rms_norm(x, nw.double(), 1e-5)
+    want = h @ w.double().t()
+    res_dev = res.to(DEV)
+    out, new_res = ops.skinny_fused(res_dev, delta.to(DEV) if with_delta else None, nw.to(DEV), 1e-5, w.to(DEV), "bf16")
+    assert torch.equal(res_dev.cpu(), res)                         # the input stream is not written
+    assert torch.equal(new_res.cpu(), x.float())
+    # the product sees x * w_norm rounded to bfloat16: one more rounding than the output's own
+    assert float((out.double().cpu() - want).abs().max()) <= 1.2e-2 * float(want.abs().max())
+    act, _ = ops.skinny_fused(res_dev, delta.to(DEV) if with_delta else None, nw.to(DEV), 1e-5, w.to(DEV), "swiglu")
+    want_act = swiglu(want[:, : N // 2], want[:, N // 2:])
+    assert float((act.double().cpu() - want_act).abs().max()) <= 1.5e-2 * float(want_act.abs().max())
+
+
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("n_q,n_kv,d,ps", [(4, 2, 16, 16), (3, 1, 32, 8), (32, 8, 64, 16), (6, 2, 48, 4)])
+def test_skinny_fused_qkv_rotation_and_cache_write(M, n_q, n_kv, d, ps):
+    """Norm, q/k/v products, rotation of neighbouring pairs and the cache write in one kernel."""
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(18)
+    K = 96 if d < 64 else 2048
+    N = (n_q + 2 * n_kv) * d
+    res = torch.randn(M, K)
+    delta = torch.randn(M, K).bfloat16()
+    nw = (1 + 0.1 * torch.randn(K)).bfloat16()
+    w = (torch.randn(N, K) / math.sqrt(K)).bfloat16()
+    positions = torch.tensor([0, 5, 63, 64, 700, 4095, 1, 17][:M], dtype=torch.int32)
+    inv = rope_inverse_frequencies(d, 500000.0, None)
+    pages = 12
+    slots = torch.randperm(pages * ps)[:M].to(torch.int32)
+    kc = torch.zeros(pages, n_kv, ps, d, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    q, new_res = ops.skinny_fused(res.to(DEV), delta.to(DEV), nw.to(DEV), 1e-5, w.to(DEV), "qkv",
+                                  rope=dict(positions=positions.to(DEV), inv_freq=inv.to(DEV), slot_mapping=slots.to(DEV),
+                                            k_cache=kc, v_cache=vc, n_q=n_q, n_kv=n_kv, head_dim=d))
+    x = res.double() + delta.double()
+    y = rms_norm(x, nw.double(), 1e-5) @ w.double().t()
+    want_q = rope_apply(y[:, : n_q * d].reshape(M, n_q, d), positions, inv, True)
+    want_k = rope_apply(y[:, n_q * d: (n_q + n_kv) * d].reshape(M, n_kv, d), positions, inv, True)
+    want_v = y[:, (n_q + n_kv) * d:].reshape(M, n_kv, d)
+    scale = float(y.abs().max())
+    assert float((q.double().cpu().reshape(M, n_q, d) - want_q).abs().max()) <= 1.5e-2 * scale
+    got_k = torch.stack([kc.cpu()[int(s) // ps, :, int(s) % ps, :] for s in slots]).double()
+    got_v = torch.stack([vc.cpu()[int(s) // ps, :, int(s) % ps, :] for s in slots]).double()
+    assert float((got_k - want_k).abs().max()) <= 1.5e-2 * scale
+    assert float((got_v - want_v).abs().max()) <= 1.5e-2 * scale
+    untouched = torch.ones(pages * ps, dtype=torch.bool)
+    untouched[slots.long()] = False
+    assert float(kc.cpu().permute(0, 2, 1, 3).reshape(pages * ps, -1)[untouched].abs().max()) == 0.0
+    assert torch.equal(new_res.cpu(), x.float())
