@@ -45,7 +45,7 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
 // the read-only path.
 __device__ __forceinline__ uint4 ld_plain16(const void* p) {
   uint4 r;
-  asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
+  asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
   return r;
 }
 
@@ -58,8 +58,10 @@ __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uin
 
 // MT: token tiles of 8.  RT: row tiles of 16 per block (1, or 2 for SwiGLU: gate, up).
 // UB: 1 doubles the loads a warp keeps in flight (for grids too small to hide latency by occupancy).
+// Registers are capped for the large-grid variant, where 68 instead of 64 would cost the fourth resident
+// block per SM (measured: the output head at 88 us instead of 84 us); the others are left to the compiler.
 template <int MT, int EPI, int UB>
-__global__ void __launch_bounds__(SK_THREADS)
+__global__ void __launch_bounds__(SK_THREADS, (MT == 1 && UB == 0 && EPI != EPI_SWIGLU) ? 4 : 0)
 skinny_gemm_kernel(const bf16* __restrict__ x, long ldx, const bf16* __restrict__ W, long ldw,
                    void* __restrict__ out, long ldo, int M, int N, int K, int I,
                    float* __restrict__ scratch, int* __restrict__ tickets) {
@@ -128,7 +130,8 @@ skinny_gemm_kernel(const bf16* __restrict__ x, long ldx, const bf16* __restrict_
     for (int u = 0; u < UNROLL; ++u) {
       const int k = (kb + u * SK_WARPS) * 32 + c * 8;
 #pragma unroll
-      for (int t = 0; t < MT; ++t) xb[u][t] = ld_plain16(xrow[t] + k);
+      for (int t = 0; t < MT; ++t)
+        xb[u][t] = UB ? ld_plain16(xrow[t] + k) : __ldg(reinterpret_cast<const uint4*>(xrow[t] + k));
     }
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u)
@@ -152,7 +155,8 @@ skinny_gemm_kernel(const bf16* __restrict__ x, long ldx, const bf16* __restrict_
     if (!waited) { pdl_wait(); waited = true; }
 #pragma unroll
     for (int t = 0; t < MT; ++t)
-      xb[t] = ok ? ld_plain16(xrow[t] + k) : make_uint4(0, 0, 0, 0);
+      xb[t] = !ok ? make_uint4(0, 0, 0, 0)
+                  : (UB ? ld_plain16(xrow[t] + k) : __ldg(reinterpret_cast<const uint4*>(xrow[t] + k)));
 #pragma unroll
     for (int r = 0; r < RT; ++r)
 #pragma unroll
@@ -240,9 +244,11 @@ static int skinny_launch(const void* x, long ldx, const void* W, long ldw, void*
   while (ks > 1 && (long)row_blocks * ks * rt * mt_pad * 128 > scratch_floats) ks /= 2;
   dim3 grid(ks, row_blocks);
   int st = 0;
-#define SK_GO(MT_)                                                                                        \
-  st = launch_pdl(skinny_gemm_kernel<MT_, EPI, 0>, grid, dim3(SK_THREADS), 0, stream, (const bf16*)x, ldx, \
-                  (const bf16*)W, ldw, out, ldo, M, N, K, I, scratch, tickets)
+  // The UB = 0 variants (large grids) read x through the read-only path and are launched fully serialised.
+#define SK_GO(MT_)                                                                                          \
+  (skinny_gemm_kernel<MT_, EPI, 0><<<grid, SK_THREADS, 0, stream>>>((const bf16*)x, ldx, (const bf16*)W, ldw, \
+                                                                    out, ldo, M, N, K, I, scratch, tickets), \
+   st = launch_status())
   if (mt <= 1 && small_grid && EPI != EPI_SWIGLU)
     st = launch_pdl(skinny_gemm_kernel<1, EPI, 1>, grid, dim3(SK_THREADS), 0, stream, (const bf16*)x, ldx,
                     (const bf16*)W, ldw, out, ldo, M, N, K, I, scratch, tickets);
