@@ -175,7 +175,7 @@ def ensure_built(modules: Iterable[object]) -> None:
 
 
 # specialisations that the build check compiles besides the plain modules (the Llama 3.2 1B shape)
-DEFAULT_SPECIALISATIONS = (("attention_flash", {"HEAD_DIM": 64}),)
+DEFAULT_SPECIALISATIONS = (("attention_flash", {"HEAD_DIM": 64}), ("attention_tc", {"HEAD_DIM": 64}))
 
 
 def build_all(verbose: bool = False) -> None:

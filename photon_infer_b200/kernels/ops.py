@@ -7,6 +7,7 @@ correctly refuses it (``UNSUPPORTED_SIZE``) instead of giving a wrong result.
 """
 from __future__ import annotations
 
+import os
 import ctypes
 from ctypes import c_float, c_int, c_long, c_void_p
 from typing import Optional
@@ -273,6 +274,49 @@ def flash_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
     if rows_mode and keys_mode:
         global _launch_count
         _launch_count += 1
+
+
+# PHOTON_ATTENTION_TC=0 keeps prompt portions on the mma.sync kernel (for comparisons)
+USE_ATTENTION_TC = os.environ.get("PHOTON_ATTENTION_TC", "1") != "0"
+
+
+def attention_tc_supported(dtype: torch.dtype, head_dim: int, group: int, page_size: int) -> bool:
+    """The tcgen05 kernel for prompt portions: bfloat16, head size 64 or 128, a group that divides
+    128 and pages of 8, 16, 32 or a multiple of 64 tokens."""
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and 1 <= group <= 128 and 128 % group == 0
+            and page_size % 8 == 0 and page_size >= 8 and (64 % page_size == 0 or page_size % 64 == 0))
+
+
+def attention_tc(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                 block_table: torch.Tensor, cu_tokens: torch.Tensor, positions: torch.Tensor,
+                 num_seqs: int, max_tokens_per_seq: int, n_q: int, n_kv: int, head_dim: int,
+                 window: Optional[int], scale: float, err: Optional[torch.Tensor]) -> None:
+    """Paged causal attention of the requests that bring more than 16 rows (tokens x heads per
+    group) in this step, on the tcgen05 tensor cores; the rows of the other requests are left
+    untouched (``flash_attention`` with ``keys_mode`` takes them)."""
+    _cuda(q, out, k_cache, v_cache, block_table, cu_tokens, positions, err)
+    T = q.shape[0]
+    if n_kv <= 0 or n_q % n_kv or not attention_tc_supported(q.dtype, head_dim, n_q // n_kv, k_cache.shape[2]):
+        raise PhotonError(ErrorCode.UNSUPPORTED_SIZE,
+                          f"attention_tc: head_dim {head_dim}, {n_q}/{n_kv} heads, pages of {k_cache.shape[2]} in {q.dtype} is not supported")
+    if q.shape[1] != n_q * head_dim or q.stride(1) != 1 or out.shape != (T, n_q * head_dim) or not out.is_contiguous():
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "attention_tc: q and out must be [T, n_q * head_dim]")
+    if out.dtype != q.dtype or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "attention_tc: q, out and the caches must be bfloat16")
+    if not k_cache.is_contiguous() or not v_cache.is_contiguous() or k_cache.shape != v_cache.shape:
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "attention_tc: the caches must be contiguous [pages, n_kv, page, d]")
+    for name, t in (("block_table", block_table), ("cu_tokens", cu_tokens), ("positions", positions)):
+        _int32(t, name)
+    if cu_tokens.numel() < num_seqs + 1 or block_table.shape[0] < num_seqs:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "attention_tc: cu_tokens and block_table must cover every request")
+    f = _fn("attention_tc", "photon_attention_tc",
+            [c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+            defines={"HEAD_DIM": head_dim})
+    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+             block_table.shape[1], _ptr(cu_tokens), _ptr(positions), int(num_seqs), int(max_tokens_per_seq), T,
+             n_q, n_kv, head_dim, k_cache.shape[2], k_cache.shape[0], int(window) if window else 0, float(scale),
+             _ptr(err), _stream()), "attention_tc")
 
 
 # ----------------------------------------------------------------------------- matrix products

@@ -46,6 +46,8 @@ class PagedAttention(Mixer):
             mods.extend(["gemm_skinny", "gemm_skinny_fused", "gemm_tc"])
         if ops.flash_attention_supported(dtype, self.head_dim):
             mods.append(("attention_flash", {"HEAD_DIM": self.head_dim}))
+        if dtype == torch.bfloat16 and self.head_dim in (64, 128) and ops.USE_ATTENTION_TC and 128 % (self.n_q // self.n_kv) == 0:
+            mods.append(("attention_tc", {"HEAD_DIM": self.head_dim}))
         return mods
 
     # -- weights: separate q/k/v in the file, one fused matrix on the device
@@ -135,7 +137,7 @@ class PagedAttention(Mixer):
         group = ctx.groups[cache.group]
         gsize = self.n_q // self.n_kv
         if ops.flash_attention_supported(q.dtype, self.head_dim):
-            # tensor cores: requests with many rows walk their keys in one block per 64 rows, requests
+            # tensor cores: requests with many rows walk their keys in one block per 128 rows, requests
             # with few rows (decoded tokens) split their keys over blocks
             T = q.shape[0]
             few = [n * gsize <= 16 for n in ctx.host_query_lens]
@@ -146,9 +148,17 @@ class PagedAttention(Mixer):
                 splits = choose_splits(sum(few) * self.n_kv, keys, 64)
                 if splits > 1:
                     scratch = torch.empty(T * self.n_q * splits * (self.head_dim + 2), dtype=torch.float32, device=q.device)
-            ops.flash_attention(q, out, cache.k, cache.v, group.block_table, ctx.cu_tokens, ctx.positions,
-                                ctx.num_seqs, ctx.max_query_len, self.n_q, self.n_kv, self.head_dim, self.window,
-                                self.scale, splits, scratch, rows_mode, keys_mode, ctx.error_flag)
+            if rows_mode and ops.USE_ATTENTION_TC and \
+                    ops.attention_tc_supported(q.dtype, self.head_dim, gsize, cache.k.shape[2]):
+                # prompt portions: tensor memory and TMA; the split-key kernel keeps the decoded tokens
+                ops.attention_tc(q, out, cache.k, cache.v, group.block_table, ctx.cu_tokens, ctx.positions,
+                                 ctx.num_seqs, ctx.max_query_len, self.n_q, self.n_kv, self.head_dim, self.window,
+                                 self.scale, ctx.error_flag)
+                rows_mode = False
+            if rows_mode or keys_mode:
+                ops.flash_attention(q, out, cache.k, cache.v, group.block_table, ctx.cu_tokens, ctx.positions,
+                                    ctx.num_seqs, ctx.max_query_len, self.n_q, self.n_kv, self.head_dim, self.window,
+                                    self.scale, splits, scratch, rows_mode, keys_mode, ctx.error_flag)
             return
         ops.paged_attention(q, out, cache.k, cache.v, group.block_table, ctx.token_seq, ctx.positions,
                             self.n_q, self.n_kv, self.head_dim, self.window, self.scale, ctx.error_flag)

@@ -585,3 +585,86 @@ def test_skinny_fused_qkv_rotation_and_cache_write(M, n_q, n_kv, d, ps):
     untouched[slots.long()] = False
     assert float(kc.cpu().permute(0, 2, 1, 3).reshape(pages * ps, -1)[untouched].abs().max()) == 0.0
     assert torch.equal(new_res.cpu(), x.float())
+
+
+def _tc_attention_case(n_q, n_kv, d, ps, window, lens, steps, seed=31, spike=None):
+    """Like _flash_case, through attention_tc for the portions (and the split-key kernel for requests with
+    few rows).  Cache slots that the step cannot see hold NaN."""
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(seed)
+    dtype = torch.bfloat16
+    pages = sum((L + ps - 1) // ps for L in lens) + 3
+    kc = torch.full((pages, n_kv, ps, d), float("nan"), dtype=dtype)
+    vc = torch.full_like(kc, float("nan"))
+    perm = torch.randperm(pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    width = max((L + ps - 1) // ps for L in lens) + 1
+    table = torch.full((len(lens), width), -1, dtype=torch.int32)
+    qs, want, positions, cu = [], [], [], [0]
+    for i, L in enumerate(lens):
+        q = torch.randn(L, n_q, d).to(dtype)
+        k = torch.randn(L, n_kv, d).to(dtype)
+        v = torch.randn(L, n_kv, d).to(dtype)
+        if spike is not None:                                   # one far key that every row must find
+            q = (0.1 * torch.randn(L, n_q, d)); k = 0.1 * torch.randn(L, n_kv, d)
+            k[spike] = 0; k[spike, :, 0] = 40.0; q[:, :, 0] = 40.0
+            q, k = q.to(dtype), k.to(dtype)
+        for lp in range((L + ps - 1) // ps):
+            table[i, lp] = perm.pop()
+        first, count = steps[i]
+        for t in range(first + count):
+            kc[table[i, t // ps], :, t % ps] = k[t]
+            vc[table[i, t // ps], :, t % ps] = v[t]
+        o = causal_attention(q.double(), k.double(), v.double(), window=window)
+        qs.append(q[first:first + count]); want.append(o[first:first + count])
+        positions += list(range(first, first + count))
+        cu.append(cu[-1] + count)
+    T = cu[-1]
+    q = torch.cat(qs).reshape(T, n_q * d)
+    out = torch.full((T, n_q * d), float("nan"), dtype=dtype, device=DEV)
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    G = n_q // n_kv
+    few = [c * G <= 16 for _, c in steps]
+    args = (q.to(DEV), out, kc.to(DEV), vc.to(DEV), table.to(DEV), torch.tensor(cu, dtype=torch.int32, device=DEV),
+            torch.tensor(positions, dtype=torch.int32, device=DEV), len(lens), max(c for _, c in steps), n_q, n_kv, d,
+            window, 1.0 / math.sqrt(d))
+    ops.attention_tc(*args, err)
+    if any(few):
+        ops.flash_attention(*args, 1, None, False, True, err)
+    assert err.cpu().tolist()[0] == 0
+    assert not torch.isnan(out.float()).any()
+    _close(out, torch.cat(want).reshape(T, n_q * d), dtype)
+    return out
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,ps,window", [
+    (4, 1, 64, 16, None), (32, 8, 64, 16, None), (8, 1, 128, 16, None), (6, 6, 64, 8, None), (16, 2, 64, 64, None),
+    (4, 2, 128, 128, None), (6, 3, 64, 32, 70), (8, 2, 128, 16, 200), (32, 8, 64, 16, 64)])
+def test_attention_tcgen05_portions(n_q, n_kv, d, ps, window):
+    """Portions from the start, in the middle and at the end of requests, of lengths that leave partial row
+    tiles and partial key tiles, beside requests with few rows that the kernel must leave alone."""
+    lens = [200, 333, 700, 1, 90, 1100]
+    steps = [(0, 200), (150, 183), (699, 1), (0, 1), (60, 30), (513, 587)]
+    _tc_attention_case(n_q, n_kv, d, ps, window, lens, steps)
+
+
+def test_attention_tcgen05_far_key_and_page_edges():
+    """A key with a dominant score at a page edge, a tile edge and the far start; every row must land on
+    its value row."""
+    for spike in (0, 15, 16, 63, 64, 127, 128, 600):
+        out = _tc_attention_case(4, 1, 64, 16, None, [700], [(640, 60)], seed=40 + spike, spike=spike)
+        assert not torch.isnan(out.float()).any()
+
+
+def test_attention_tcgen05_refuses_other_sizes():
+    from photon_infer_b200.errors import PhotonError
+    from photon_infer_b200.kernels import ops
+    assert not ops.attention_tc_supported(torch.bfloat16, 80, 4, 16)
+    assert not ops.attention_tc_supported(torch.bfloat16, 64, 3, 16)
+    assert not ops.attention_tc_supported(torch.bfloat16, 64, 4, 4)
+    assert not ops.attention_tc_supported(torch.float32, 64, 4, 16)
+    q = torch.zeros(32, 3 * 64, dtype=torch.bfloat16, device=DEV)
+    kc = torch.zeros(4, 1, 16, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(PhotonError):
+        ops.attention_tc(q, torch.empty_like(q), kc, kc.clone(), torch.zeros(1, 4, dtype=torch.int32, device=DEV),
+                         torch.tensor([0, 32], dtype=torch.int32, device=DEV), torch.arange(32, dtype=torch.int32, device=DEV),
+                         1, 32, 3, 1, 64, None, 0.125, None)
