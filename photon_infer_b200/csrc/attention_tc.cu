@@ -1,8 +1,9 @@
 // Paged causal attention for prompt portions on the fifth-generation tensor cores
 // (tcgen05, accumulators in tensor memory), bfloat16, head size 64 or 128.
 //
-// A block owns 128 query rows of one request that share a key/value head
-// (row = token_in_step * GROUP + head_in_group, as in attention_flash.cu) and walks the
+// A block owns up to 128 query rows of one request that share a key/value head
+// (row = token_in_step * GROUP + head_in_group, as in attention_flash.cu; floor(128 / GROUP)
+// whole tokens) and walks the
 // request's keys in tiles of 64:
 //   * warp 4 brings the rows of Q (one 3-D TMA box) and then the key and value tiles of the
 //     paged cache (one TMA box per page part, the block table followed by the lanes of the
@@ -62,7 +63,7 @@ struct AttnTcParams {
   const int* block_table; int max_pages;           // [S, max_pages]
   const int* cu_tokens;                            // [S + 1]
   const int* positions;                            // [T]
-  int n_kv, group, page_size, num_pages, box_rows, window, tiles_per_seq, total_rows;
+  int n_kv, group, tile_rows, page_size, num_pages, box_rows, window, tiles_per_seq, total_rows;
   float scale_log2;
   int* err;
 };
@@ -71,6 +72,22 @@ __device__ __forceinline__ float at_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// Two 32-bit lanes per instruction (sm_100): d = a * b + c and d = a + b on pairs.
+__device__ __forceinline__ void at_fma2(float& d0, float& d1, float a0, float a1, float b, float c) {
+  asm("{\n.reg .b64 ra, rb, rc, rd;\nmov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %4};\nmov.b64 rc, {%5, %5};\n"
+      "fma.rn.f32x2 rd, ra, rb, rc;\nmov.b64 {%0, %1}, rd;\n}"
+      : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void at_add2(float& d0, float& d1, float a0, float a1) {
+  asm("{\n.reg .b64 ra, rd;\nmov.b64 ra, {%2, %3};\nmov.b64 rd, {%0, %1};\n"
+      "add.rn.f32x2 rd, rd, ra;\nmov.b64 {%0, %1}, rd;\n}"
+      : "+f"(d0), "+f"(d1) : "f"(a0), "f"(a1));
+}
+__device__ __forceinline__ float at_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 __device__ __forceinline__ uint32_t at_pack(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -87,9 +104,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const int G = P.group;
   const int tok0 = P.cu_tokens[seq], ntok = P.cu_tokens[seq + 1] - tok0;
   const int rows = ntok * G;
-  const int row0 = qtile * AT_ROWS;
+  const int row0 = qtile * P.tile_rows;            // tile_rows: the largest multiple of GROUP up to 128
   if (rows <= 16 || row0 >= rows) return;          // few rows: the split-key kernel takes this request
-  const int nrows = min(AT_ROWS, rows - row0);
+  const int nrows = min(P.tile_rows, rows - row0);
   const int t_first = row0 / G, t_last = (row0 + nrows - 1) / G;
   const int pos_first = P.positions[tok0 + t_first], pos_last = P.positions[tok0 + t_last];
   const int key_lo = (P.window > 0 && pos_first - P.window + 1 > 0) ? pos_first - P.window + 1 : 0;
@@ -132,7 +149,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   if (warp == 4) {
     // ---------------- producer
     if (lane == 0) {
-      tc_mbar_expect_tx(q_full, AT_Q_BYTES);
+      tc_mbar_expect_tx(q_full, P.tile_rows * 128 * AT_DH);       // rows beyond tile_rows stay as they are: nobody uses them
 #pragma unroll
       for (int h = 0; h < AT_DH; ++h)
         tc_tma_load3(q_s + h * (AT_ROWS * 128), &map_q, h * 64, g * G, tok0 + t_first, q_full);
@@ -142,6 +159,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     int issued = 0;
     for (int i = 0; i < ntiles; ++i) {
       const int s = i % AT_STAGES;
+      // the page of this lane's part, looked up before the wait for a free stage
+      int rowc = P.total_rows;                      // outside the map: the part is filled with zeros
+      if (lane < boxes) {
+        const int key = (tile_begin + i) * AT_KT + lane * P.box_rows;
+        if (key <= pos_last && key + P.box_rows - 1 >= key_lo) {
+          const int pidx = key / P.page_size, slot = key - pidx * P.page_size;
+          const int page = table[pidx];
+          if (page < 0 || page >= P.num_pages) report_error(P.err, PHOTON_DEV_BAD_PAGE, tok0, key, page);
+          else rowc = (page * P.n_kv + g) * P.page_size + slot;
+        }
+      }
       int ok = 1;
       if (lane == 0) ok = tc_wait(&kv_empty[s], ((i / AT_STAGES) & 1) ^ 1, abort_flag) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -149,14 +177,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (lane == 0) { tc_mbar_expect_tx(&k_full[s], AT_KV_BYTES); tc_mbar_expect_tx(&v_full[s], AT_KV_BYTES); }
       __syncwarp();
       if (lane < boxes) {
-        const int key = (tile_begin + i) * AT_KT + lane * P.box_rows;
-        int rowc = P.total_rows;                    // outside the map: the part is filled with zeros
-        if (key <= pos_last && key + P.box_rows - 1 >= key_lo) {
-          const int pidx = key / P.page_size, slot = key - pidx * P.page_size;
-          const int page = table[pidx];
-          if (page < 0 || page >= P.num_pages) report_error(P.err, PHOTON_DEV_BAD_PAGE, tok0, key, page);
-          else rowc = (page * P.n_kv + g) * P.page_size + slot;
-        }
         unsigned char* kst = kv_s + s * 2 * AT_KV_BYTES + lane * P.box_rows * 128;
         unsigned char* vst = kst + AT_KV_BYTES;
 #pragma unroll
@@ -214,7 +234,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // ---------------- softmax: thread = row
     const int r = threadIdx.x;                      // 0..127
     const int row = row0 + r;
-    const bool valid = row < rows;
+    const bool valid = r < P.tile_rows && row < rows;
     const int pos = valid ? P.positions[tok0 + row / G] : -1;
     const int lo = (P.window > 0 && pos - P.window + 1 > 0) ? pos - P.window + 1 : 0;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
@@ -234,19 +254,22 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       tc_ld32_issue(lane_addr + b * AT_KT + 32, sv + 32);
       tc_ld_wait();
       const int key_base = (tile_begin + i) * AT_KT;
-      float mx = -INFINITY;
-      if (key_base + AT_KT - 1 <= pos && key_base >= lo) {
-#pragma unroll
-        for (int j = 0; j < AT_KT; ++j) mx = fmaxf(mx, __uint_as_float(sv[j]));
-      } else {
+      if (!(key_base + AT_KT - 1 <= pos && key_base >= lo)) {
 #pragma unroll
         for (int j = 0; j < AT_KT; ++j) {
           const int key = key_base + j;
-          const float v = (key >= lo && key <= pos) ? __uint_as_float(sv[j]) : -INFINITY;
-          sv[j] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
+          sv[j] = (key >= lo && key <= pos) ? sv[j] : 0xff800000u;       // -inf
         }
       }
+      // four independent chains of three-input maxima
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < AT_KT; j += 8) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          mx4[u] = at_max3(mx4[u], __uint_as_float(sv[j + 2 * u]), __uint_as_float(sv[j + 2 * u + 1]));
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // the maximum in use lags behind the true one by at most AT_RESCALE_STEP
       const float cand = fmaxf(m_used, mx * c);
       float factor = 1.f;
@@ -254,15 +277,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (grow) { factor = at_exp2(m_used - cand); m_used = cand; l *= factor; }
       const float sub = (m_used == -INFINITY) ? 0.f : m_used;
       uint32_t pk[AT_KT / 2];
-      float sum = 0.f;
+      float sum8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      const float nsub = -sub;
 #pragma unroll
       for (int j = 0; j < AT_KT; j += 2) {
-        const float p0 = at_exp2(fmaf(__uint_as_float(sv[j]), c, -sub));
-        const float p1 = at_exp2(fmaf(__uint_as_float(sv[j + 1]), c, -sub));
-        sum += p0 + p1;
+        float x0, x1;
+        at_fma2(x0, x1, __uint_as_float(sv[j]), __uint_as_float(sv[j + 1]), c, nsub);
+        const float p0 = at_exp2(x0), p1 = at_exp2(x1);
+        at_add2(sum8[j & 6], sum8[(j & 6) + 1], p0, p1);
         pk[j >> 1] = at_pack(p0, p1);
       }
-      l += sum;
+      l += ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
       // O rescale: the products of the tile before must have landed
       if (i > 0 && __any_sync(0xffffffffu, grow)) {
         if (!wait_all(&pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1)) { ok = false; break; }
@@ -338,8 +363,8 @@ PHOTON_API int photon_attention_tc_head_dim() { return HEAD_DIM; }
 
 // Runs the requests of the step that bring more than 16 rows (tokens x group); the others are left
 // untouched.  q [T, n_q * d] with row stride q_stride, out [T, n_q * d]; k_cache, v_cache
-// [num_pages, n_kv, page_size, d] contiguous.  group must divide 128, page_size must be a multiple
-// of 8 that divides 64 or is a multiple of 64.
+// [num_pages, n_kv, page_size, d] contiguous.  group at most 128, page_size a multiple of 8 that
+// divides 64 or is a multiple of 64.
 PHOTON_API int photon_attention_tc(const void* q, long q_stride, void* out, long out_stride, const void* k_cache,
                                    const void* v_cache, const int* block_table, int max_pages, const int* cu_tokens,
                                    const int* positions, int S, int max_tokens_per_seq, int T, int n_q, int n_kv, int d,
@@ -348,7 +373,7 @@ PHOTON_API int photon_attention_tc(const void* q, long q_stride, void* out, long
   if (S <= 0 || T <= 0) return 0;
   if (d != HEAD_DIM || n_kv <= 0 || n_q % n_kv || !(scale > 0.f)) return PHOTON_ERR_UNSUPPORTED;
   const int G = n_q / n_kv;
-  if (G > AT_ROWS || AT_ROWS % G) return PHOTON_ERR_UNSUPPORTED;
+  if (G > AT_ROWS) return PHOTON_ERR_UNSUPPORTED;
   if (page_size < 8 || (page_size & 7) || !((AT_KT % page_size) == 0 || (page_size % AT_KT) == 0)) return PHOTON_ERR_UNSUPPORTED;
   if (((uintptr_t)q & 15) || (q_stride & 7) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) ||
       ((uintptr_t)out & 15) || (out_stride & 7))
@@ -375,11 +400,12 @@ PHOTON_API int photon_attention_tc(const void* q, long q_stride, void* out, long
   if (st != 0) return st;
   AttnTcParams P;
   P.out = (bf16*)out; P.out_stride = out_stride; P.block_table = block_table; P.max_pages = max_pages;
-  P.cu_tokens = cu_tokens; P.positions = positions; P.n_kv = n_kv; P.group = G; P.page_size = page_size;
+  P.cu_tokens = cu_tokens; P.positions = positions; P.n_kv = n_kv; P.group = G; P.tile_rows = (AT_ROWS / G) * G;
+  P.page_size = page_size;
   P.num_pages = num_pages; P.box_rows = box_rows; P.window = window; P.total_rows = (int)total_rows;
   P.scale_log2 = scale * 1.4426950408889634f; P.err = err;
   const long rows = (long)max_tokens_per_seq * G;
-  P.tiles_per_seq = (int)((rows + AT_ROWS - 1) / AT_ROWS);
+  P.tiles_per_seq = (int)((rows + P.tile_rows - 1) / P.tile_rows);
   if ((long)S * P.tiles_per_seq > 65535) return PHOTON_ERR_UNSUPPORTED;
   static bool attr_done = false;
   if (!attr_done) {

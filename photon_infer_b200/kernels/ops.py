@@ -281,9 +281,9 @@ USE_ATTENTION_TC = os.environ.get("PHOTON_ATTENTION_TC", "1") != "0"
 
 
 def attention_tc_supported(dtype: torch.dtype, head_dim: int, group: int, page_size: int) -> bool:
-    """The tcgen05 kernel for prompt portions: bfloat16, head size 64 or 128, a group that divides
-    128 and pages of 8, 16, 32 or a multiple of 64 tokens."""
-    return (dtype == torch.bfloat16 and head_dim in (64, 128) and 1 <= group <= 128 and 128 % group == 0
+    """The tcgen05 kernel for prompt portions: bfloat16, head size 64 or 128, up to 128 heads per
+    key/value head and pages of 8, 16, 32 or a multiple of 64 tokens."""
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and 1 <= group <= 128
             and page_size % 8 == 0 and page_size >= 8 and (64 % page_size == 0 or page_size % 64 == 0))
 
 

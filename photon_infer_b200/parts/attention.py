@@ -46,7 +46,7 @@ class PagedAttention(Mixer):
             mods.extend(["gemm_skinny", "gemm_skinny_fused", "gemm_tc"])
         if ops.flash_attention_supported(dtype, self.head_dim):
             mods.append(("attention_flash", {"HEAD_DIM": self.head_dim}))
-        if dtype == torch.bfloat16 and self.head_dim in (64, 128) and ops.USE_ATTENTION_TC and 128 % (self.n_q // self.n_kv) == 0:
+        if dtype == torch.bfloat16 and self.head_dim in (64, 128) and ops.USE_ATTENTION_TC and self.n_q // self.n_kv <= 128:
             mods.append(("attention_tc", {"HEAD_DIM": self.head_dim}))
         return mods
 

@@ -638,7 +638,8 @@ def _tc_attention_case(n_q, n_kv, d, ps, window, lens, steps, seed=31, spike=Non
 
 @pytest.mark.parametrize("n_q,n_kv,d,ps,window", [
     (4, 1, 64, 16, None), (32, 8, 64, 16, None), (8, 1, 128, 16, None), (6, 6, 64, 8, None), (16, 2, 64, 64, None),
-    (4, 2, 128, 128, None), (6, 3, 64, 32, 70), (8, 2, 128, 16, 200), (32, 8, 64, 16, 64)])
+    (4, 2, 128, 128, None), (6, 3, 64, 32, 70), (8, 2, 128, 16, 200), (32, 8, 64, 16, 64), (6, 2, 128, 16, None), (5, 1, 64, 16, None),
+    (7, 1, 64, 8, 33)])
 def test_attention_tcgen05_portions(n_q, n_kv, d, ps, window):
     """Portions from the start, in the middle and at the end of requests, of lengths that leave partial row
     tiles and partial key tiles, beside requests with few rows that the kernel must leave alone."""
@@ -659,11 +660,11 @@ def test_attention_tcgen05_refuses_other_sizes():
     from photon_infer_b200.errors import PhotonError
     from photon_infer_b200.kernels import ops
     assert not ops.attention_tc_supported(torch.bfloat16, 80, 4, 16)
-    assert not ops.attention_tc_supported(torch.bfloat16, 64, 3, 16)
+    assert not ops.attention_tc_supported(torch.bfloat16, 64, 129, 16)
     assert not ops.attention_tc_supported(torch.bfloat16, 64, 4, 4)
     assert not ops.attention_tc_supported(torch.float32, 64, 4, 16)
     q = torch.zeros(32, 3 * 64, dtype=torch.bfloat16, device=DEV)
-    kc = torch.zeros(4, 1, 16, 64, dtype=torch.bfloat16, device=DEV)
+    kc = torch.zeros(4, 1, 4, 64, dtype=torch.bfloat16, device=DEV)            # pages of 4 tokens
     with pytest.raises(PhotonError):
         ops.attention_tc(q, torch.empty_like(q), kc, kc.clone(), torch.zeros(1, 4, dtype=torch.int32, device=DEV),
                          torch.tensor([0, 32], dtype=torch.int32, device=DEV), torch.arange(32, dtype=torch.int32, device=DEV),
