@@ -44,6 +44,15 @@ TINY: Dict[str, dict] = {
                     layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"],
                     bos_token_id=3, eos_token_id=4),
         seed=2, init_std=0.08, norm_std=0.2, block_size=16),
+    # heads of 64 (the size the tensor-memory attention kernel takes), three query heads per key/value
+    # head, a window on the first layer, half-split rotation pairs, pages of 32
+    "tiny_d": dict(
+        config=dict(architectures=["LlamaForCausalLM"], hidden_size=160, intermediate_size=208,
+                    num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2, head_dim=64,
+                    vocab_size=301, max_position_embeddings=1024, rms_norm_eps=2e-5, rope_theta=100000.0,
+                    rope_scaling=None, tie_word_embeddings=True, sliding_window=40,
+                    layer_types=["sliding_attention", "full_attention"], bos_token_id=1, eos_token_id=2),
+        seed=3, init_std=0.06, norm_std=0.15, block_size=32),
 }
 
 

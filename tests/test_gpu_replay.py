@@ -14,7 +14,7 @@ from helpers import TINY, TOL, TraceSession, make_model_folder, plain_logits, ra
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"tiny_a": [70, 150, 33, 200, 97, 260], "tiny_b": [45, 130, 64, 210, 31, 99],
-           "tiny_c": [90, 300, 40, 170, 65, 230]}
+           "tiny_c": [90, 300, 40, 170, 65, 230], "tiny_d": [120, 290, 36, 180, 75, 250]}
 PORTIONS = [7, 2, 16, 3, 2, 33, 5, 2, 64, 11, 2, 17]
 
 
