@@ -200,7 +200,6 @@ flash_attention_kernel(const FlashParams P) {
   bf16* kv = qs + (KEYS_MODE ? 16 : FA_ROWS) * FA_LD;                      // FA_STAGES x (K | V) x 64 x FA_LD
   __shared__ int s_flag;
 
-  pdl_launch_dependents();
   pdl_wait();
   const int split = blockIdx.x, g = blockIdx.y;
   // row tiles are handed out last-first: the tiles with the most keys to walk start first
@@ -320,6 +319,7 @@ flash_attention_kernel(const FlashParams P) {
     __syncthreads();                                                       // the stage may be overwritten
   }
   cp_async_wait<0>();
+  pdl_launch_dependents();                         // the next kernel may be scheduled while the results are merged
 
   // the quad's partial sums
 #pragma unroll

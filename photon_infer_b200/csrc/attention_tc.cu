@@ -102,6 +102,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const int seq = blockIdx.y / P.tiles_per_seq;
   const int qtile = P.tiles_per_seq - 1 - (blockIdx.y - seq * P.tiles_per_seq);   // most keys first
   const int G = P.group;
+  pdl_wait();                                      // q, the cache and the step's tables come from kernels before
   const int tok0 = P.cu_tokens[seq], ntok = P.cu_tokens[seq + 1] - tok0;
   const int rows = ntok * G;
   const int row0 = qtile * P.tile_rows;            // tile_rows: the largest multiple of GROUP up to 128
@@ -229,6 +230,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         tc_commit(&kv_empty[s]);
         tc_commit(&pv_done[i & 1]);
       }
+      pdl_launch_dependents();                      // all products of this block are issued
     }
   } else {
     // ---------------- softmax: thread = row
@@ -416,6 +418,5 @@ PHOTON_API int photon_attention_tc(const void* q, long q_stride, void* out, long
     attr_done = true;
   }
   dim3 grid(n_kv, S * P.tiles_per_seq);
-  attention_tc_kernel<<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(map_q, map_k, map_v, P);
-  return launch_status();
+  return launch_pdl(attention_tc_kernel, grid, dim3(AT_THREADS), (size_t)AT_SMEM_BYTES, stream, map_q, map_k, map_v, P);
 }

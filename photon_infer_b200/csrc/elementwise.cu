@@ -64,7 +64,6 @@ __global__ void add_rmsnorm_kernel(const TD* delta, float* residual,          //
                                    TO* out, const int* rows, int H, float eps) {  // read-only path for them
   __shared__ float red[32];
   extern __shared__ __align__(16) float stash[];               // H floats: the summed row
-  pdl_launch_dependents();
   pdl_wait();
   const int r = rows ? rows[blockIdx.x] : blockIdx.x;
   float* res = residual + (size_t)r * H;
@@ -92,6 +91,7 @@ __global__ void add_rmsnorm_kernel(const TD* delta, float* residual,          //
     }
   }
   ss = block_sum(ss, red);
+  pdl_launch_dependents();                         // the next kernel may be scheduled while the row is written
   const float inv = 1.0f / sqrtf(ss / (float)H + eps);
   TO* o = out + (size_t)blockIdx.x * H;
   if (VEC) {

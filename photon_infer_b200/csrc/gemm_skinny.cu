@@ -112,7 +112,6 @@ skinny_gemm_kernel(const bf16* __restrict__ x, long ldx, const bf16* __restrict_
   int kb = kb0 + warp;
   // The weights do not depend on the kernel before this one: their first loads are issued, then the
   // kernel waits for its predecessor (whose output is x), so the wait overlaps the memory latency.
-  pdl_launch_dependents();
   bool waited = false;
   // whole rounds: every load is issued before the first product, no predicates
   for (; kb + (UNROLL - 1) * SK_WARPS < full_blocks; kb += SK_WARPS * UNROLL) {
@@ -167,6 +166,9 @@ skinny_gemm_kernel(const bf16* __restrict__ x, long ldx, const bf16* __restrict_
   }
 
   if (!waited) pdl_wait();
+  // The next kernel may be scheduled once every block has come this far (not earlier: its blocks would
+  // take the places of blocks of this grid that have not started yet).
+  pdl_launch_dependents();
   // add the warps' partial sums in warp order
 #pragma unroll
   for (int r = 0; r < RT; ++r)

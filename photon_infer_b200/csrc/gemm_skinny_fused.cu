@@ -125,7 +125,6 @@ skinny_fused_kernel(const SkinnyFusedArgs A) {
   const int nblocks = (A.K + 31) >> 5;
   const int full_blocks = A.K >> 5;
   int kb = warp;
-  pdl_launch_dependents();
   bool waited = false;
   for (; kb + (SF_UNROLL - 1) * SF_WARPS < full_blocks; kb += SF_WARPS * SF_UNROLL) {
     uint4 wa[SF_UNROLL][RT][2], xb[SF_UNROLL];
@@ -165,6 +164,7 @@ skinny_fused_kernel(const SkinnyFusedArgs A) {
     }
   }
   if (!waited) pdl_wait();
+  pdl_launch_dependents();                         // after the main loop: see gemm_skinny.cu
 
   // sum of squares of token g: over the four lanes that share it, then over the warps
   ss += __shfl_xor_sync(0xffffffffu, ss, 1);

@@ -80,6 +80,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();                                     // A is the output of the kernel before; the set-up above overlapped its tail
 
   if (warp == 0) {
     // ---------------- producer: one lane issues the TMA loads, the ring runs on across tiles
@@ -136,6 +137,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         if (ok) tc_commit(&acc_ready[buf]);         // the accumulator is complete once all products are done
       }
+      pdl_launch_dependents();                      // all products of this block are issued
     }
   } else {
     // ---------------- epilogue: warps 2..5 own TMEM lanes 32 * (warp % 4) .. + 31
@@ -241,14 +243,11 @@ PHOTON_API int photon_gemm_tc(const void* x, long ldx, const void* W, long ldw, 
   }
   switch (epilogue) {
     case TC_EPI_BF16:
-      gemm_tc_kernel<TC_EPI_BF16><<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(map_a, map_w, out, ldo, M, N, K, I, tiles_n, num_tiles, err);
-      break;
+      return launch_pdl(gemm_tc_kernel<TC_EPI_BF16>, grid, dim3(TC_THREADS), (size_t)TC_SMEM_BYTES, stream, map_a, map_w, out, ldo, M, N, K, I, tiles_n, num_tiles, err);
     case TC_EPI_F32:
-      gemm_tc_kernel<TC_EPI_F32><<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(map_a, map_w, out, ldo, M, N, K, I, tiles_n, num_tiles, err);
-      break;
+      return launch_pdl(gemm_tc_kernel<TC_EPI_F32>, grid, dim3(TC_THREADS), (size_t)TC_SMEM_BYTES, stream, map_a, map_w, out, ldo, M, N, K, I, tiles_n, num_tiles, err);
     case TC_EPI_SWIGLU:
-      gemm_tc_kernel<TC_EPI_SWIGLU><<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(map_a, map_w, out, ldo, M, N, K, I, tiles_n, num_tiles, err);
-      break;
+      return launch_pdl(gemm_tc_kernel<TC_EPI_SWIGLU>, grid, dim3(TC_THREADS), (size_t)TC_SMEM_BYTES, stream, map_a, map_w, out, ldo, M, N, K, I, tiles_n, num_tiles, err);
     default:
       return PHOTON_ERR_ARGUMENT;
   }

@@ -88,8 +88,8 @@ rope_kv_write_vec_kernel(bf16* q, long q_stride, bf16* k, long k_stride, const b
                          const int* __restrict__ slot_mapping, bf16* __restrict__ k_cache,
                          bf16* __restrict__ v_cache, int n_q, int n_kv, int d, int page_size, long num_slots,
                          int rotate, int write_kv, int* err) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.y;
   const int per_head = d >> 4;                               // items per head
   const int item = blockIdx.x * blockDim.x + threadIdx.x;
