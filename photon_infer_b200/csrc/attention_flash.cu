@@ -37,6 +37,7 @@
 #define FA_KEYS_THREADS 128               // KEYS mode: four warps, 16 keys of every tile each
 #define FA_ROWS_THREADS (FA_ROWS * 2)
 #define FA_STAGES 3
+#define FA_TABLE_SMEM 256                 // block-table entries the KEYS kernel copies to shared memory up front
 #define FA_LD (HEAD_DIM + 8)              // padded row length in shared memory (elements): conflict-free ldmatrix
 #define FA_KD (HEAD_DIM / 16)             // k-steps over the head dimension
 #define FA_ND (HEAD_DIM / 8)              // n-tiles over the head dimension
@@ -80,6 +81,8 @@ struct FlashParams {
   const int* block_table; int max_pages;  // [S, max_pages]
   const int* cu_tokens;                   // [S + 1] first token of each request in the step
   const int* positions;                   // [T]
+  const int* context_lens;                // [S] or null: tokens of the request after this step; when given, the
+                                          // KEYS kernel takes a request's positions as context_len - n .. context_len - 1
   float* part_acc; float* part_ml; int* tickets;   // scratch of the KEYS mode with splits
   int n_q, n_kv, group, page_size, page_shift, num_pages, window, num_splits, tiles_per_seq;   // page_shift: log2(page_size) or -1
   float scale_log2;                       // scale * log2(e)
@@ -88,10 +91,12 @@ struct FlashParams {
 
 // Copies the keys [key0, key0 + 64) of key/value head g into one stage (K tile, then V tile).
 // Rows outside [lo, hi] or without a page are filled with zeros.
-__device__ __forceinline__ void load_kv_tile(const FlashParams& P, const int* table, int g, int key0, int lo,
-                                             int hi, bf16* ks, bf16* vs, int t_for_err) {
+// tid, nthreads: the calling thread's index in the group of threads that share this stage, and the group's size.
+__device__ __forceinline__ void load_kv_tile(const FlashParams& P, const int* table, const int* table_s, int g,
+                                             int key0, int lo, int hi, bf16* ks, bf16* vs, int t_for_err,
+                                             int tid, int nthreads) {
   constexpr int CPR = HEAD_DIM / 8;                       // 16-byte chunks per row
-  for (int c = threadIdx.x; c < FA_TILE_K * CPR; c += blockDim.x) {
+  for (int c = tid; c < FA_TILE_K * CPR; c += nthreads) {
     const int r = c / CPR, cc = c - r * CPR;
     const int key = key0 + r;
     bool valid = key >= lo && key <= hi;
@@ -99,7 +104,7 @@ __device__ __forceinline__ void load_kv_tile(const FlashParams& P, const int* ta
     if (valid) {
       const int pidx = P.page_shift >= 0 ? (key >> P.page_shift) : key / P.page_size;
       const int slot = P.page_shift >= 0 ? (key & (P.page_size - 1)) : key - pidx * P.page_size;
-      const int page = table[pidx];
+      const int page = (table_s != nullptr && pidx < FA_TABLE_SMEM) ? table_s[pidx] : table[pidx];
       if (page < 0 || page >= P.num_pages) {
         if (cc == 0) report_error(P.err, PHOTON_DEV_BAD_PAGE, t_for_err, key, page);
         valid = false;
@@ -192,31 +197,56 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qa)[FA_KD][4], const 
   }
 }
 
-template <bool KEYS_MODE>
-__global__ void __launch_bounds__(KEYS_MODE ? FA_KEYS_THREADS : FA_ROWS_THREADS, KEYS_MODE ? 3 : (FA_ROWS >= 128 ? 2 : 3))
+// NSUB (KEYS mode): groups of four warps in a block; each group walks its own share of the block's key
+// tiles with a ring of stages of its own, and the groups' results are merged through shared memory like
+// the warps' (one block per SM then does what NSUB blocks with a merge through global memory would).
+template <bool KEYS_MODE, int NSUB>
+__global__ void __launch_bounds__(KEYS_MODE ? FA_KEYS_THREADS * NSUB : FA_ROWS_THREADS,
+                                  KEYS_MODE ? (NSUB == 1 ? 3 : 1) : (FA_ROWS >= 128 ? 2 : 3))
 flash_attention_kernel(const FlashParams P) {
   extern __shared__ __align__(16) unsigned char fa_dyn[];
-  bf16* qs = reinterpret_cast<bf16*>(fa_dyn);                              // (KEYS: 16, ROWS: FA_ROWS) x FA_LD
-  bf16* kv = qs + (KEYS_MODE ? 16 : FA_ROWS) * FA_LD;                      // FA_STAGES x (K | V) x 64 x FA_LD
+  constexpr int Q_ELEMS = (KEYS_MODE ? 16 : FA_ROWS) * FA_LD;
+  constexpr int RING_ELEMS = FA_STAGES * 2 * FA_TILE_K * FA_LD;
+  const int sub = KEYS_MODE ? (int)(threadIdx.x >> 7) : 0;                  // group of four warps
+  const int stid = KEYS_MODE ? (int)(threadIdx.x & 127) : (int)threadIdx.x; // thread index inside the group
+  const int sthreads = KEYS_MODE ? FA_KEYS_THREADS : FA_ROWS_THREADS;
+  // per group: Q rows (KEYS: 16, ROWS: FA_ROWS) x FA_LD, then FA_STAGES x (K | V) x 64 x FA_LD
+  bf16* qs = reinterpret_cast<bf16*>(fa_dyn) + (size_t)sub * (Q_ELEMS + RING_ELEMS);
+  bf16* kv = qs + Q_ELEMS;
+  auto group_sync = [&]() {
+    if (KEYS_MODE && NSUB > 1) asm volatile("bar.sync %0, 128;" ::"r"(sub + 1) : "memory");
+    else __syncthreads();
+  };
   __shared__ int s_flag;
 
+  __shared__ int table_s[KEYS_MODE ? FA_TABLE_SMEM : 1];
   pdl_wait();
   const int split = blockIdx.x, g = blockIdx.y;
   // row tiles are handed out last-first: the tiles with the most keys to walk start first
   const int seq = blockIdx.z / P.tiles_per_seq, qtile = P.tiles_per_seq - 1 - (blockIdx.z - seq * P.tiles_per_seq);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int wq = warp & 3;                                                  // KEYS: the warp's quarter of a key tile
   const int G = P.group;
-  const int tok0 = P.cu_tokens[seq], ntok = P.cu_tokens[seq + 1] - tok0;
+  const int* table = P.block_table + (size_t)seq * P.max_pages;
+  if (KEYS_MODE) {
+    // The request's block-table row goes to shared memory in the same round trip as its token range and
+    // length: the key loads then depend on one memory latency, not on three in a row.
+    for (int i = threadIdx.x; i < min(P.max_pages, FA_TABLE_SMEM); i += blockDim.x) table_s[i] = table[i];
+  }
+  const int tok0 = P.cu_tokens[seq], tok1 = P.cu_tokens[seq + 1];
+  const int ctx_len = (KEYS_MODE && P.context_lens != nullptr) ? P.context_lens[seq] : -1;
+  const int ntok = tok1 - tok0;
   const int rows = ntok * G;
   if ((rows <= 16) != KEYS_MODE) return;                                   // the other launch takes this request
   const int row0 = KEYS_MODE ? 0 : qtile * FA_ROWS;
   if (row0 >= rows || (KEYS_MODE && qtile > 0)) return;
   const int nrows = min(KEYS_MODE ? 16 : FA_ROWS, rows - row0);
-  const int* table = P.block_table + (size_t)seq * P.max_pages;
+  const bool by_len = KEYS_MODE && ctx_len >= 0;                           // positions follow from the length
 
   // positions of the tile's first and last token bound the keys the block needs
   const int tfirst = row0 / G, tlast = (row0 + nrows - 1) / G;
-  const int pos_first = P.positions[tok0 + tfirst], pos_last = P.positions[tok0 + tlast];
+  const int pos_first = by_len ? ctx_len - ntok + tfirst : P.positions[tok0 + tfirst];
+  const int pos_last = by_len ? ctx_len - ntok + tlast : P.positions[tok0 + tlast];
   const int key_lo = (P.window > 0 && pos_first - P.window + 1 > 0) ? pos_first - P.window + 1 : 0;
   int tile_begin = key_lo / FA_TILE_K, tile_end = pos_last / FA_TILE_K + 1;     // key tiles [begin, end)
   if (KEYS_MODE && P.num_splits > 1) {
@@ -224,13 +254,21 @@ flash_attention_kernel(const FlashParams P) {
     tile_begin += split * per;
     tile_end = min(tile_end, tile_begin + per);
   }
+  if (KEYS_MODE && NSUB > 1) {
+    // the block's tiles are dealt to its groups in order
+    const int per = (max(0, tile_end - tile_begin) + NSUB - 1) / NSUB;
+    tile_begin += sub * per;
+    tile_end = min(tile_end, tile_begin + per);
+  }
   const int ntiles = max(0, tile_end - tile_begin);
+  if (KEYS_MODE) __syncthreads();                                          // table_s is complete
+  const int* tsm = KEYS_MODE ? table_s : nullptr;
 
   // ---- Q rows into shared memory (zeros beyond the valid rows)
   {
     constexpr int CPR = HEAD_DIM / 8;
     const int qrows = KEYS_MODE ? 16 : FA_ROWS;
-    for (int c = threadIdx.x; c < qrows * CPR; c += blockDim.x) {
+    for (int c = stid; c < qrows * CPR; c += sthreads) {                   // KEYS: every group has a copy of its own
       const int r = c / CPR, cc = c - r * CPR;
       const int row = row0 + r;
       const bool valid = row < rows;
@@ -244,7 +282,7 @@ flash_attention_kernel(const FlashParams P) {
   // prologue: the first FA_STAGES - 1 tiles (the Q copy joins the first group)
 #pragma unroll
   for (int i = 0; i < FA_STAGES - 1; ++i) {
-    if (i < ntiles) load_kv_tile(P, table, g, (tile_begin + i) * FA_TILE_K, key_lo, pos_last, stage_k(i), stage_v(i), tok0);
+    if (i < ntiles) load_kv_tile(P, table, tsm, g, (tile_begin + i) * FA_TILE_K, key_lo, pos_last, stage_k(i), stage_v(i), tok0, stid, sthreads);
     cp_async_commit();
   }
 
@@ -255,7 +293,7 @@ flash_attention_kernel(const FlashParams P) {
   for (int h2 = 0; h2 < 2; ++h2) {
     const int row = row0 + wrow + (lane >> 2) + h2 * 8;
     if (row < rows) {
-      pos_r[h2] = P.positions[tok0 + row / G];
+      pos_r[h2] = by_len ? ctx_len - ntok + row / G : P.positions[tok0 + row / G];
       lo_r[h2] = (P.window > 0 && pos_r[h2] - P.window + 1 > 0) ? pos_r[h2] - P.window + 1 : 0;
     } else {
       pos_r[h2] = -1; lo_r[h2] = 0;                                        // sees nothing
@@ -282,12 +320,12 @@ flash_attention_kernel(const FlashParams P) {
     {
       const int nx = i + FA_STAGES - 1;
       if (nx < ntiles)
-        load_kv_tile(P, table, g, (tile_begin + nx) * FA_TILE_K, key_lo, pos_last, stage_k(nx % FA_STAGES),
-                     stage_v(nx % FA_STAGES), tok0);
+        load_kv_tile(P, table, tsm, g, (tile_begin + nx) * FA_TILE_K, key_lo, pos_last, stage_k(nx % FA_STAGES),
+                     stage_v(nx % FA_STAGES), tok0, stid, sthreads);
       cp_async_commit();
     }
     cp_async_wait<FA_STAGES - 1>();
-    __syncthreads();
+    group_sync();
     if (i == 0) {
 #pragma unroll
       for (int kd = 0; kd < FA_KD; ++kd)
@@ -297,13 +335,13 @@ flash_attention_kernel(const FlashParams P) {
     const int key_base = (tile_begin + i) * FA_TILE_K;
     if (KEYS_MODE) {
       // every warp takes 16 keys of the tile
-      const int k0 = key_base + warp * 16;
+      const int k0 = key_base + wq * 16;
       if (k0 <= warp_pos_max) {
         if (k0 + 15 <= warp_pos_min && k0 >= warp_lo_max)
-          warp_tile<2, false>(qa, stage_k(st), stage_v(st), warp * 16, key_base, pos_r[0], pos_r[1], lo_r[0], lo_r[1],
+          warp_tile<2, false>(qa, stage_k(st), stage_v(st), wq * 16, key_base, pos_r[0], pos_r[1], lo_r[0], lo_r[1],
                               P.scale_log2, m, l, o);
         else
-          warp_tile<2, true>(qa, stage_k(st), stage_v(st), warp * 16, key_base, pos_r[0], pos_r[1], lo_r[0], lo_r[1],
+          warp_tile<2, true>(qa, stage_k(st), stage_v(st), wq * 16, key_base, pos_r[0], pos_r[1], lo_r[0], lo_r[1],
                              P.scale_log2, m, l, o);
       }
     } else {
@@ -316,7 +354,7 @@ flash_attention_kernel(const FlashParams P) {
                              P.scale_log2, m, l, o);
       }
     }
-    __syncthreads();                                                       // the stage may be overwritten
+    group_sync();                                                          // the stage may be overwritten
   }
   cp_async_wait<0>();
   pdl_launch_dependents();                         // the next kernel may be scheduled while the results are merged
@@ -343,11 +381,12 @@ flash_attention_kernel(const FlashParams P) {
     return;
   }
 
-  // ---- KEYS mode: merge the four warps (each saw a quarter of the keys) through shared memory
-  __syncthreads();                                                         // all warps are done with the ring
-  float* wm = reinterpret_cast<float*>(kv);                                // [4][16]
-  float* wl = wm + 4 * 16;                                                 // [4][16]
-  float* wo = wl + 4 * 16;                                                 // [4][16][HEAD_DIM]
+  // ---- KEYS mode: merge the warps (each saw its own keys) through shared memory, in warp order
+  constexpr int NW = 4 * NSUB;
+  __syncthreads();                                                         // all warps are done with the rings
+  float* wm = reinterpret_cast<float*>(fa_dyn);                            // [NW][16]
+  float* wl = wm + NW * 16;                                                // [NW][16]
+  float* wo = wl + NW * 16;                                                // [NW][16][HEAD_DIM]
 #pragma unroll
   for (int h2 = 0; h2 < 2; ++h2) {
     const int r = (lane >> 2) + h2 * 8;
@@ -364,11 +403,11 @@ flash_attention_kernel(const FlashParams P) {
     const int r = e / HEAD_DIM, d = e - r * HEAD_DIM;
     float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) M = fmaxf(M, wm[w * 16 + r]);
+    for (int w = 0; w < NW; ++w) M = fmaxf(M, wm[w * 16 + r]);
     float L = 0.f, A = 0.f;
     if (M != -INFINITY) {
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
+      for (int w = 0; w < NW; ++w) {
         const float mw = wm[w * 16 + r];
         const float sc = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
         L += wl[w * 16 + r] * sc;
@@ -415,18 +454,27 @@ flash_attention_kernel(const FlashParams P) {
 }
 
 PHOTON_API int photon_flash_attention_head_dim() { return HEAD_DIM; }
+// Groups of four warps (each with a ring of stages of its own) that fit into the shared memory of one block.
+constexpr int FA_GROUP_BYTES = (16 * FA_LD + FA_STAGES * 2 * FA_TILE_K * FA_LD) * 2;
+constexpr int FA_MAX_GROUPS = (4 * FA_GROUP_BYTES + 2048 <= 232448) ? 4 : ((2 * FA_GROUP_BYTES + 2048 <= 232448) ? 2 : 1);
+PHOTON_API int photon_flash_attention_max_groups() { return FA_MAX_GROUPS; }
 
 // mode bit 0: launch the ROWS kernel (requests with more than 16 rows); bit 1: the KEYS kernel (at most 16
 // rows = tokens * group).  max_tokens_per_seq bounds the tokens any request brings in this step.
+// nsub: 1, 2 or 4 groups of four warps per block of the KEYS kernel, each walking its own share of the block's
+// key tiles (at most photon_flash_attention_max_groups(), which depends on the head size).
+// context_lens (may be null): tokens of each request after this step; with it the KEYS kernel does not read
+// `positions` (the tokens a request brings are then taken to be its last ones, in order).
 // Scratch (KEYS mode with num_splits > 1): part_acc float [T * n_q * num_splits * d], part_ml float
 // [T * n_q * num_splits * 2], tickets int [S * n_kv] all zero between launches.  Launches that share scratch
 // must not overlap on the device.
 PHOTON_API int photon_flash_attention(const void* q, long q_stride, void* out, long out_stride, const void* k_cache,
                                       const void* v_cache, const int* block_table, int max_pages,
-                                      const int* cu_tokens, const int* positions, float* part_acc, float* part_ml,
+                                      const int* cu_tokens, const int* positions, const int* context_lens,
+                                      float* part_acc, float* part_ml,
                                       int* tickets, int S, int max_tokens_per_seq, int n_q, int n_kv, int d,
                                       int page_size, int num_pages, int window, float scale, int num_splits,
-                                      int mode, int* err, cudaStream_t stream) {
+                                      int nsub, int mode, int* err, cudaStream_t stream) {
   if (S <= 0) return 0;
   if (d != HEAD_DIM || n_kv <= 0 || n_q % n_kv || !(scale > 0.f)) return PHOTON_ERR_UNSUPPORTED;
   if (((uintptr_t)q % 16) || ((size_t)q_stride * 2) % 16 || ((uintptr_t)k_cache % 16) || ((uintptr_t)v_cache % 16))
@@ -437,6 +485,7 @@ PHOTON_API int photon_flash_attention(const void* q, long q_stride, void* out, l
   P.q = (const bf16*)q; P.q_stride = q_stride; P.out = (bf16*)out; P.out_stride = out_stride;
   P.k_cache = (const bf16*)k_cache; P.v_cache = (const bf16*)v_cache;
   P.block_table = block_table; P.max_pages = max_pages; P.cu_tokens = cu_tokens; P.positions = positions;
+  P.context_lens = context_lens;
   P.part_acc = part_acc; P.part_ml = part_ml; P.tickets = tickets;
   P.n_q = n_q; P.n_kv = n_kv; P.group = n_q / n_kv; P.page_size = page_size; P.num_pages = num_pages;
   P.page_shift = -1;
@@ -444,18 +493,27 @@ PHOTON_API int photon_flash_attention(const void* q, long q_stride, void* out, l
   P.window = window; P.scale_log2 = scale * 1.4426950408889634f; P.err = err;
   const size_t ring = (size_t)FA_STAGES * 2 * FA_TILE_K * FA_LD;
   const size_t smem_rows = ((size_t)FA_ROWS * FA_LD + ring) * sizeof(bf16);
-  const size_t smem_keys = ((size_t)16 * FA_LD + ring) * sizeof(bf16);
+  const size_t smem_keys = ((size_t)16 * FA_LD + ring) * sizeof(bf16);      // per group of four warps
+  if (nsub != 1 && nsub != 2 && nsub != 4) return PHOTON_ERR_ARGUMENT;
+  if (nsub > photon_flash_attention_max_groups()) return PHOTON_ERR_UNSUPPORTED;
   static bool attr_done = false;
   if (!attr_done) {
     // room for several blocks per SM: the largest shared-memory carve-out
-    cudaError_t e1 = cudaFuncSetAttribute(flash_attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rows);
-    cudaError_t e2 = cudaFuncSetAttribute(flash_attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_keys);
-    cudaError_t e3 = cudaFuncSetAttribute(flash_attention_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    cudaError_t e4 = cudaFuncSetAttribute(flash_attention_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    if (e1 != cudaSuccess) return (int)e1;
-    if (e2 != cudaSuccess) return (int)e2;
-    if (e3 != cudaSuccess) return (int)e3;
-    if (e4 != cudaSuccess) return (int)e4;
+    cudaError_t e[8];
+    e[0] = cudaFuncSetAttribute(flash_attention_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rows);
+    e[1] = cudaFuncSetAttribute(flash_attention_kernel<false, 1>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    e[2] = cudaFuncSetAttribute(flash_attention_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_keys);
+    e[3] = cudaFuncSetAttribute(flash_attention_kernel<true, 1>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    e[4] = e[5] = e[6] = e[7] = cudaSuccess;
+    if (photon_flash_attention_max_groups() >= 2) {
+      e[4] = cudaFuncSetAttribute(flash_attention_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * smem_keys));
+      e[5] = cudaFuncSetAttribute(flash_attention_kernel<true, 2>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    }
+    if (photon_flash_attention_max_groups() >= 4) {
+      e[6] = cudaFuncSetAttribute(flash_attention_kernel<true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(4 * smem_keys));
+      e[7] = cudaFuncSetAttribute(flash_attention_kernel<true, 4>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    }
+    for (int i = 0; i < 8; ++i) if (e[i] != cudaSuccess) return (int)e[i];
     attr_done = true;
   }
   if (mode & 1) {
@@ -464,7 +522,7 @@ PHOTON_API int photon_flash_attention(const void* q, long q_stride, void* out, l
     P.num_splits = 1;
     if ((long)S * P.tiles_per_seq > 65535) return PHOTON_ERR_UNSUPPORTED;
     dim3 grid(1, n_kv, S * P.tiles_per_seq);
-    int st = launch_pdl(flash_attention_kernel<false>, grid, dim3(FA_ROWS_THREADS), smem_rows, stream, P);
+    int st = launch_pdl(flash_attention_kernel<false, 1>, grid, dim3(FA_ROWS_THREADS), smem_rows, stream, P);
     if (st != 0) return st;
   }
   if (mode & 2) {
@@ -472,7 +530,14 @@ PHOTON_API int photon_flash_attention(const void* q, long q_stride, void* out, l
     P.num_splits = num_splits;
     if (S > 65535) return PHOTON_ERR_UNSUPPORTED;
     dim3 grid(num_splits, n_kv, S);
-    return launch_pdl(flash_attention_kernel<true>, grid, dim3(FA_KEYS_THREADS), smem_keys, stream, P);
+    if (nsub == 4) {
+      if constexpr (FA_MAX_GROUPS >= 4)
+        return launch_pdl(flash_attention_kernel<true, 4>, grid, dim3(FA_KEYS_THREADS * 4), 4 * smem_keys, stream, P);
+    } else if (nsub == 2) {
+      if constexpr (FA_MAX_GROUPS >= 2)
+        return launch_pdl(flash_attention_kernel<true, 2>, grid, dim3(FA_KEYS_THREADS * 2), 2 * smem_keys, stream, P);
+    }
+    return launch_pdl(flash_attention_kernel<true, 1>, grid, dim3(FA_KEYS_THREADS), smem_keys, stream, P);
   }
   return 0;
 }

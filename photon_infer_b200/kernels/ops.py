@@ -229,16 +229,32 @@ def flash_attention_supported(dtype: torch.dtype, head_dim: int) -> bool:
     return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
 
 
+def flash_attention_max_groups(head_dim: int) -> int:
+    """Groups of four warps that the split-key kernel can run in one block at this head size (4, 2 or 1)."""
+    lib = load_module("attention_flash", {"HEAD_DIM": head_dim})
+    return int(lib.photon_flash_attention_max_groups())
+
+
 def flash_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     block_table: torch.Tensor, cu_tokens: torch.Tensor, positions: torch.Tensor,
                     num_seqs: int, max_tokens_per_seq: int, n_q: int, n_kv: int, head_dim: int,
                     window: Optional[int], scale: float, num_splits: int, scratch: Optional[torch.Tensor],
-                    rows_mode: bool, keys_mode: bool, err: Optional[torch.Tensor]) -> None:
+                    rows_mode: bool, keys_mode: bool, err: Optional[torch.Tensor],
+                    context_lens: Optional[torch.Tensor] = None, key_groups: int = 1) -> None:
     """Paged causal attention on the tensor cores.  ``cu_tokens [S + 1]`` gives each request's
     tokens in the step.  ``rows_mode``: run requests with more than 16 rows (tokens x heads per
     group); ``keys_mode``: run the others, their keys split over ``num_splits`` blocks.
-    ``scratch``: float32, at least ``T * n_q * num_splits * (head_dim + 2)`` when ``num_splits > 1``."""
-    _cuda(q, out, k_cache, v_cache, block_table, cu_tokens, positions, scratch, err)
+    ``scratch``: float32, at least ``T * n_q * num_splits * (head_dim + 2)`` when ``num_splits > 1``.
+    ``context_lens [S]`` (optional): tokens of each request after this step; the split-key kernel then
+    derives positions from it (a request's tokens of the step are its last ones) and saves a round trip.
+    ``key_groups``: 1, 2 or 4 groups of four warps per block of the split-key kernel, each walking its own
+    share of the block's keys (``flash_attention_max_groups`` bounds it); their results are merged in shared
+    memory, which is far cheaper than the merge of ``num_splits`` blocks through global memory."""
+    _cuda(q, out, k_cache, v_cache, block_table, cu_tokens, positions, scratch, err, context_lens)
+    if context_lens is not None:
+        _int32(context_lens, "context_lens")
+        if context_lens.numel() < num_seqs:
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, "flash_attention: context_lens must cover every request")
     T = q.shape[0]
     if not flash_attention_supported(q.dtype, head_dim) or n_kv <= 0 or n_q % n_kv:
         raise PhotonError(ErrorCode.UNSUPPORTED_SIZE, f"flash_attention: head_dim {head_dim} in {q.dtype} is not supported")
@@ -264,13 +280,15 @@ def flash_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
     mode = (1 if rows_mode else 0) | (2 if keys_mode else 0)
     f = _fn("attention_flash", "photon_flash_attention",
             [c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
-             c_void_p, c_void_p],
+             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+             c_int, c_void_p, c_void_p],
             defines={"HEAD_DIM": head_dim})
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
-             block_table.shape[1], _ptr(cu_tokens), _ptr(positions), _ptr(part_acc), _ptr(part_ml), _ptr(tickets),
+             block_table.shape[1], _ptr(cu_tokens), _ptr(positions), _ptr(context_lens), _ptr(part_acc), _ptr(part_ml),
+             _ptr(tickets),
              int(num_seqs), int(max_tokens_per_seq), n_q, n_kv, head_dim, k_cache.shape[2], k_cache.shape[0],
-             int(window) if window else 0, float(scale), splits, mode, _ptr(err), _stream()), "flash_attention")
+             int(window) if window else 0, float(scale), splits, int(key_groups) if keys_mode else 1, mode, _ptr(err),
+             _stream()), "flash_attention")
     if rows_mode and keys_mode:
         global _launch_count
         _launch_count += 1

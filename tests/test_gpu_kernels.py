@@ -429,12 +429,28 @@ def _flash_case(n_q, n_kv, d, ps, window, lens, steps, splits, seed=21):
     G = n_q // n_kv
     few = [c * G <= 16 for _, c in steps]
     scratch = torch.full((T * n_q * splits * (d + 2),), float("nan"), device=DEV)
-    ops.flash_attention(q.to(DEV), out, kc.to(DEV), vc.to(DEV), table.to(DEV), torch.tensor(cu, dtype=torch.int32, device=DEV),
-                        torch.tensor(positions, dtype=torch.int32, device=DEV), len(lens), max(c for _, c in steps),
-                        n_q, n_kv, d, window, 1.0 / math.sqrt(d), splits, scratch, not all(few), any(few), err)
+    args = (q.to(DEV), out, kc.to(DEV), vc.to(DEV), table.to(DEV), torch.tensor(cu, dtype=torch.int32, device=DEV),
+            torch.tensor(positions, dtype=torch.int32, device=DEV), len(lens), max(c for _, c in steps),
+            n_q, n_kv, d, window, 1.0 / math.sqrt(d), splits, scratch, not all(few), any(few), err)
+    ops.flash_attention(*args)
     assert err.cpu().tolist()[0] == 0
     assert not torch.isnan(out.float()).any()
     _close(out, torch.cat(want).reshape(T, n_q * d), dtype)
+    # the same with the requests' lengths given: the split-key kernel then does not read the positions
+    first = out.clone()
+    out.fill_(float("nan"))
+    lens_after = torch.tensor([f + c for f, c in steps], dtype=torch.int32, device=DEV)
+    ops.flash_attention(*args, lens_after)
+    assert err.cpu().tolist()[0] == 0
+    assert torch.equal(out, first)
+    # and with the keys of a block dealt to groups of warps
+    for groups in (2, 4):
+        if groups <= ops.flash_attention_max_groups(d):
+            out.fill_(float("nan"))
+            ops.flash_attention(*args, lens_after, groups)
+            assert err.cpu().tolist()[0] == 0
+            assert not torch.isnan(out.float()).any()
+            _close(out, torch.cat(want).reshape(T, n_q * d), dtype)
 
 
 @pytest.mark.parametrize("n_q,n_kv,d,ps,window", [

@@ -152,3 +152,17 @@ def test_abort():
     assert cache.live_requests() == [b]
     s.abort(b)
     assert not s.has_work() and cache.free_pages() == [64]
+
+
+def test_key_shares_of_decoded_tokens():
+    """Blocks and groups of warps per (request, key/value head): groups while every pair can have an SM,
+    blocks on top only for long contexts, one group and about 256 blocks beyond."""
+    from photon_infer_b200.parts.attention import choose_key_shares
+    assert choose_key_shares(64, 640, 4) == (1, 4)          # batch 8, 8 key/value heads
+    assert choose_key_shares(64, 4096, 4) == (2, 4)
+    assert choose_key_shares(8, 8192, 4) == (8, 4)          # batch 1
+    assert choose_key_shares(128, 640, 4) == (1, 4)
+    assert choose_key_shares(512, 640, 4) == (1, 1)         # batch 64
+    assert choose_key_shares(160, 4096, 4) == (2, 1)
+    assert choose_key_shares(64, 640, 1) == (4, 1)          # a head size with room for one group only
+    assert choose_key_shares(1, 30, 4) == (1, 4)
