@@ -36,7 +36,9 @@
 #endif
 #define FA_KEYS_THREADS 128               // KEYS mode: four warps, 16 keys of every tile each
 #define FA_ROWS_THREADS (FA_ROWS * 2)
+#ifndef FA_STAGES
 #define FA_STAGES 3
+#endif
 #define FA_TABLE_SMEM 256                 // block-table entries the KEYS kernel copies to shared memory up front
 #define FA_LD (HEAD_DIM + 8)              // padded row length in shared memory (elements): conflict-free ldmatrix
 #define FA_KD (HEAD_DIM / 16)             // k-steps over the head dimension
@@ -200,17 +202,19 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qa)[FA_KD][4], const 
 // NSUB (KEYS mode): groups of four warps in a block; each group walks its own share of the block's key
 // tiles with a ring of stages of its own, and the groups' results are merged through shared memory like
 // the warps' (one block per SM then does what NSUB blocks with a merge through global memory would).
-template <bool KEYS_MODE, int NSUB>
+// STAGES: depth of a group's ring of key/value tiles.  Three keep a block's loads two tiles ahead; two make
+// room for five blocks per SM instead of three, which pays when there are more blocks than places.
+template <bool KEYS_MODE, int NSUB, int STAGES>
 __global__ void __launch_bounds__(KEYS_MODE ? FA_KEYS_THREADS * NSUB : FA_ROWS_THREADS,
-                                  KEYS_MODE ? (NSUB == 1 ? 3 : 1) : (FA_ROWS >= 128 ? 2 : 3))
+                                  KEYS_MODE ? (NSUB == 1 ? (STAGES == 2 ? 4 : 3) : 1) : (FA_ROWS >= 128 ? 2 : 3))
 flash_attention_kernel(const FlashParams P) {
   extern __shared__ __align__(16) unsigned char fa_dyn[];
   constexpr int Q_ELEMS = (KEYS_MODE ? 16 : FA_ROWS) * FA_LD;
-  constexpr int RING_ELEMS = FA_STAGES * 2 * FA_TILE_K * FA_LD;
+  constexpr int RING_ELEMS = STAGES * 2 * FA_TILE_K * FA_LD;
   const int sub = KEYS_MODE ? (int)(threadIdx.x >> 7) : 0;                  // group of four warps
   const int stid = KEYS_MODE ? (int)(threadIdx.x & 127) : (int)threadIdx.x; // thread index inside the group
   const int sthreads = KEYS_MODE ? FA_KEYS_THREADS : FA_ROWS_THREADS;
-  // per group: Q rows (KEYS: 16, ROWS: FA_ROWS) x FA_LD, then FA_STAGES x (K | V) x 64 x FA_LD
+  // per group: Q rows (KEYS: 16, ROWS: FA_ROWS) x FA_LD, then STAGES x (K | V) x 64 x FA_LD
   bf16* qs = reinterpret_cast<bf16*>(fa_dyn) + (size_t)sub * (Q_ELEMS + RING_ELEMS);
   bf16* kv = qs + Q_ELEMS;
   auto group_sync = [&]() {
@@ -279,9 +283,9 @@ flash_attention_kernel(const FlashParams P) {
   }
   auto stage_k = [&](int st) { return kv + (size_t)st * 2 * FA_TILE_K * FA_LD; };
   auto stage_v = [&](int st) { return kv + (size_t)st * 2 * FA_TILE_K * FA_LD + FA_TILE_K * FA_LD; };
-  // prologue: the first FA_STAGES - 1 tiles (the Q copy joins the first group)
+  // prologue: the first STAGES - 1 tiles (the Q copy joins the first group)
 #pragma unroll
-  for (int i = 0; i < FA_STAGES - 1; ++i) {
+  for (int i = 0; i < STAGES - 1; ++i) {
     if (i < ntiles) load_kv_tile(P, table, tsm, g, (tile_begin + i) * FA_TILE_K, key_lo, pos_last, stage_k(i), stage_v(i), tok0, stid, sthreads);
     cp_async_commit();
   }
@@ -316,22 +320,22 @@ flash_attention_kernel(const FlashParams P) {
   uint32_t qa[FA_KD][4];
 
   for (int i = 0; i < ntiles; ++i) {
-    // keep FA_STAGES - 1 tiles in flight
+    // keep STAGES - 1 tiles in flight
     {
-      const int nx = i + FA_STAGES - 1;
+      const int nx = i + STAGES - 1;
       if (nx < ntiles)
-        load_kv_tile(P, table, tsm, g, (tile_begin + nx) * FA_TILE_K, key_lo, pos_last, stage_k(nx % FA_STAGES),
-                     stage_v(nx % FA_STAGES), tok0, stid, sthreads);
+        load_kv_tile(P, table, tsm, g, (tile_begin + nx) * FA_TILE_K, key_lo, pos_last, stage_k(nx % STAGES),
+                     stage_v(nx % STAGES), tok0, stid, sthreads);
       cp_async_commit();
     }
-    cp_async_wait<FA_STAGES - 1>();
+    cp_async_wait<STAGES - 1>();
     group_sync();
     if (i == 0) {
 #pragma unroll
       for (int kd = 0; kd < FA_KD; ++kd)
         ldsm4(qa[kd], qs + (wrow + (lane & 15)) * FA_LD + kd * 16 + ((lane >> 4) << 3));
     }
-    const int st = i % FA_STAGES;
+    const int st = i % STAGES;
     const int key_base = (tile_begin + i) * FA_TILE_K;
     if (KEYS_MODE) {
       // every warp takes 16 keys of the tile
@@ -492,28 +496,32 @@ PHOTON_API int photon_flash_attention(const void* q, long q_stride, void* out, l
   for (int sh = 0; sh < 20; ++sh) if ((1 << sh) == page_size) P.page_shift = sh;
   P.window = window; P.scale_log2 = scale * 1.4426950408889634f; P.err = err;
   const size_t ring = (size_t)FA_STAGES * 2 * FA_TILE_K * FA_LD;
+  const size_t ring2 = (size_t)2 * 2 * FA_TILE_K * FA_LD;                   // two stages
   const size_t smem_rows = ((size_t)FA_ROWS * FA_LD + ring) * sizeof(bf16);
   const size_t smem_keys = ((size_t)16 * FA_LD + ring) * sizeof(bf16);      // per group of four warps
+  const size_t smem_keys2 = ((size_t)16 * FA_LD + ring2) * sizeof(bf16);
   if (nsub != 1 && nsub != 2 && nsub != 4) return PHOTON_ERR_ARGUMENT;
   if (nsub > photon_flash_attention_max_groups()) return PHOTON_ERR_UNSUPPORTED;
   static bool attr_done = false;
   if (!attr_done) {
     // room for several blocks per SM: the largest shared-memory carve-out
-    cudaError_t e[8];
-    e[0] = cudaFuncSetAttribute(flash_attention_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rows);
-    e[1] = cudaFuncSetAttribute(flash_attention_kernel<false, 1>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    e[2] = cudaFuncSetAttribute(flash_attention_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_keys);
-    e[3] = cudaFuncSetAttribute(flash_attention_kernel<true, 1>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    cudaError_t e[10];
+    e[0] = cudaFuncSetAttribute(flash_attention_kernel<false, 1, FA_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rows);
+    e[1] = cudaFuncSetAttribute(flash_attention_kernel<false, 1, FA_STAGES>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    e[2] = cudaFuncSetAttribute(flash_attention_kernel<true, 1, FA_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_keys);
+    e[3] = cudaFuncSetAttribute(flash_attention_kernel<true, 1, FA_STAGES>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    e[8] = cudaFuncSetAttribute(flash_attention_kernel<true, 1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_keys2);
+    e[9] = cudaFuncSetAttribute(flash_attention_kernel<true, 1, 2>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     e[4] = e[5] = e[6] = e[7] = cudaSuccess;
     if (photon_flash_attention_max_groups() >= 2) {
-      e[4] = cudaFuncSetAttribute(flash_attention_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * smem_keys));
-      e[5] = cudaFuncSetAttribute(flash_attention_kernel<true, 2>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+      e[4] = cudaFuncSetAttribute(flash_attention_kernel<true, 2, FA_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * smem_keys));
+      e[5] = cudaFuncSetAttribute(flash_attention_kernel<true, 2, FA_STAGES>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     }
     if (photon_flash_attention_max_groups() >= 4) {
-      e[6] = cudaFuncSetAttribute(flash_attention_kernel<true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(4 * smem_keys));
-      e[7] = cudaFuncSetAttribute(flash_attention_kernel<true, 4>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+      e[6] = cudaFuncSetAttribute(flash_attention_kernel<true, 4, FA_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(4 * smem_keys));
+      e[7] = cudaFuncSetAttribute(flash_attention_kernel<true, 4, FA_STAGES>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     }
-    for (int i = 0; i < 8; ++i) if (e[i] != cudaSuccess) return (int)e[i];
+    for (int i = 0; i < 10; ++i) if (e[i] != cudaSuccess) return (int)e[i];
     attr_done = true;
   }
   if (mode & 1) {
@@ -522,7 +530,7 @@ PHOTON_API int photon_flash_attention(const void* q, long q_stride, void* out, l
     P.num_splits = 1;
     if ((long)S * P.tiles_per_seq > 65535) return PHOTON_ERR_UNSUPPORTED;
     dim3 grid(1, n_kv, S * P.tiles_per_seq);
-    int st = launch_pdl(flash_attention_kernel<false, 1>, grid, dim3(FA_ROWS_THREADS), smem_rows, stream, P);
+    int st = launch_pdl(flash_attention_kernel<false, 1, FA_STAGES>, grid, dim3(FA_ROWS_THREADS), smem_rows, stream, P);
     if (st != 0) return st;
   }
   if (mode & 2) {
@@ -532,12 +540,23 @@ PHOTON_API int photon_flash_attention(const void* q, long q_stride, void* out, l
     dim3 grid(num_splits, n_kv, S);
     if (nsub == 4) {
       if constexpr (FA_MAX_GROUPS >= 4)
-        return launch_pdl(flash_attention_kernel<true, 4>, grid, dim3(FA_KEYS_THREADS * 4), 4 * smem_keys, stream, P);
+        return launch_pdl(flash_attention_kernel<true, 4, FA_STAGES>, grid, dim3(FA_KEYS_THREADS * 4), 4 * smem_keys, stream, P);
     } else if (nsub == 2) {
       if constexpr (FA_MAX_GROUPS >= 2)
-        return launch_pdl(flash_attention_kernel<true, 2>, grid, dim3(FA_KEYS_THREADS * 2), 2 * smem_keys, stream, P);
+        return launch_pdl(flash_attention_kernel<true, 2, FA_STAGES>, grid, dim3(FA_KEYS_THREADS * 2), 2 * smem_keys, stream, P);
     }
-    return launch_pdl(flash_attention_kernel<true, 1>, grid, dim3(FA_KEYS_THREADS), smem_keys, stream, P);
+    // more blocks than the places that rings of three stages leave (three per SM at heads of 64): rings of two stages
+    // (measured at 32/8 heads of 64, 640 keys, batch 64: 22.0 us against 31.6 us)
+    static int places3 = 0;
+    if (places3 == 0) {
+      int dev = 0, sms = 0;
+      cudaGetDevice(&dev);
+      if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+      places3 = sms * (int)(232448 / (smem_keys + 1024));                  // blocks that fit by shared memory
+    }
+    if ((long)num_splits * n_kv * S > places3)
+      return launch_pdl(flash_attention_kernel<true, 1, 2>, grid, dim3(FA_KEYS_THREADS), smem_keys2, stream, P);
+    return launch_pdl(flash_attention_kernel<true, 1, FA_STAGES>, grid, dim3(FA_KEYS_THREADS), smem_keys, stream, P);
   }
   return 0;
 }
