@@ -28,7 +28,7 @@ CSRC_DIR = os.path.dirname(os.path.abspath(__file__))
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-shared", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden"]
-ALL_MODULES = ("elementwise", "rope_kv", "attention", "gemm_f32", "gemm_skinny", "gemm_skinny_fused", "gemm_skinny_static", "gemm_tc", "sampling")
+ALL_MODULES = ("elementwise", "rope_kv", "attention", "gemm_f32", "gemm_skinny", "gemm_skinny_fused", "gemm_skinny_static", "gemm_tc", "gemm_tc2", "sampling")
 
 _loaded: Dict[Tuple[str, Tuple[Tuple[str, str], ...]], ctypes.CDLL] = {}
 _lock = threading.Lock()

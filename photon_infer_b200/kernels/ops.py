@@ -456,7 +456,7 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
         skinny_gemm(x, w_gate_up, out, "swiglu")
         return out
     if gemm_tc_supported(x, w_gate_up) and gemm_tc_tiles(M, 2 * I, swiglu=True) >= TC_MIN_TILES:
-        gemm_tc(x, w_gate_up, out, "swiglu")
+        gemm_tc(x, w_gate_up, out, "swiglu", pair=M >= TC_PAIR_MIN_ROWS)
         return out
     swiglu(linear(x, w_gate_up), out)
     return out
@@ -475,6 +475,7 @@ def _error_word(device) -> Optional[torch.Tensor]:
 
 
 TC_MIN_TILES = 96           # below this many 128 x 256 tiles the tcgen05 product leaves too many SMs idle
+TC_PAIR_MIN_ROWS = 256      # from here on tiles of 256 x 256 on pairs of SMs (gemm_tc2.cu): a third less operand traffic
 
 
 def gemm_tc_tiles(M: int, N: int, swiglu: bool = False) -> int:
@@ -493,10 +494,11 @@ def gemm_tc_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str = "bf16",
-            err: Optional[torch.Tensor] = None) -> None:
+            err: Optional[torch.Tensor] = None, pair: bool = False) -> None:
     """``out = x @ weight^T`` on the tcgen05 tensor cores (TMA operands, accumulator in tensor memory).
     ``epilogue``: ``"bf16"``, ``"f32"`` or ``"swiglu"`` (``weight`` holds gate rows then up rows; ``out``
-    is ``[M, I]``)."""
+    is ``[M, I]``).  ``pair``: tiles of 256 x 256 on pairs of SMs (``gemm_tc2.cu``) instead of 128 x 256
+    on one."""
     _cuda(x, weight, out, err)
     M, K = x.shape
     N = weight.shape[0]
@@ -507,12 +509,13 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: 
         raise PhotonError(ErrorCode.UNSUPPORTED_SIZE, "gemm_tc: needs bfloat16, K a multiple of 8 and aligned rows")
     if out.shape != (M, cols) or out.dtype != want or out.stride(1) != 1:
         raise PhotonError(ErrorCode.SHAPE_MISMATCH, f"gemm_tc: out must be {want} [{M}, {cols}]")
-    f = _fn("gemm_tc", "photon_gemm_tc",
+    module, entry = ("gemm_tc2", "photon_gemm_tc2") if pair else ("gemm_tc", "photon_gemm_tc")
+    f = _fn(module, entry,
             [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     if err is None:
         err = _error_word(x.device)
     _check(f(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), out.stride(0), M, N, K, code,
-             _ptr(err), _stream()), "gemm_tc")
+             _ptr(err), _stream()), module)
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
@@ -538,7 +541,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = 
             and gemm_tc_tiles(M, N) >= TC_MIN_TILES and (out is None or out.stride(1) == 1):
         if out is None:
             out = torch.empty((M, N), dtype=want, device=x.device)
-        gemm_tc(x, weight, out, "f32" if want == torch.float32 else "bf16")
+        gemm_tc(x, weight, out, "f32" if want == torch.float32 else "bf16", pair=M >= TC_PAIR_MIN_ROWS)
         return out
     if x.dtype == torch.float32:
         if want != torch.float32:

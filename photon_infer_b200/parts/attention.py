@@ -44,7 +44,7 @@ class PagedAttention(Mixer):
     def required_kernels(self, dtype):
         mods = list(self.kernel_modules)
         if dtype == torch.bfloat16:
-            mods.extend(["gemm_skinny", "gemm_skinny_fused", "gemm_tc"])
+            mods.extend(["gemm_skinny", "gemm_skinny_fused", "gemm_tc", "gemm_tc2"])
         if ops.flash_attention_supported(dtype, self.head_dim):
             mods.append(("attention_flash", {"HEAD_DIM": self.head_dim}))
         if dtype == torch.bfloat16 and self.head_dim in (64, 128) and ops.USE_ATTENTION_TC and self.n_q // self.n_kv <= 128:

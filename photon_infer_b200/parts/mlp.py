@@ -17,7 +17,7 @@ class SwiGLUFeedForward(FeedForward):
     kernel_modules = ("elementwise",)
 
     def required_kernels(self, dtype):
-        return ["elementwise"] + (["gemm_skinny", "gemm_skinny_fused", "gemm_tc"] if dtype == torch.bfloat16 else [])
+        return ["elementwise"] + (["gemm_skinny", "gemm_skinny_fused", "gemm_tc", "gemm_tc2"] if dtype == torch.bfloat16 else [])
 
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden_size = hidden_size

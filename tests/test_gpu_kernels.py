@@ -685,3 +685,30 @@ def test_attention_tcgen05_refuses_other_sizes():
         ops.attention_tc(q, torch.empty_like(q), kc, kc.clone(), torch.zeros(1, 4, dtype=torch.int32, device=DEV),
                          torch.tensor([0, 32], dtype=torch.int32, device=DEV), torch.arange(32, dtype=torch.int32, device=DEV),
                          1, 32, 3, 1, 64, None, 0.125, None)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (1, 8, 8), (100, 300, 72), (257, 513, 520), (2048, 3072, 2048),
+                                   (333, 389, 120), (4096, 256, 8192), (129, 129, 136)])
+def test_gemm_tcgen05_pairs_of_sms(M, N, K):
+    """The product on pairs of SMs (cta_group::2) against float64, with partial tiles on every side."""
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(16)
+    x = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).bfloat16()
+    want = x.double() @ w.double().t()
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_tc(x, w, out32, "f32", err, pair=True)
+    assert err.cpu().tolist()[0] == 0
+    assert float((out32.double() - want).abs().max()) <= 2e-6 * math.sqrt(K) * float(want.abs().max())
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc(x, w, out, "bf16", err, pair=True)
+    assert err.cpu().tolist()[0] == 0
+    _close(out, want, torch.bfloat16)
+    if N % 2 == 0:
+        I = N // 2
+        act = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.gemm_tc(x, w, act, "swiglu", err, pair=True)
+        assert err.cpu().tolist()[0] == 0
+        g, u = want[:, :I], want[:, I:]
+        _close(act, g / (1 + torch.exp(-g)) * u, torch.bfloat16)
