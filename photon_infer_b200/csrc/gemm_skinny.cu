@@ -60,13 +60,15 @@ __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uin
 // UB: 1 doubles the loads a warp keeps in flight (for grids too small to hide latency by occupancy).
 // Registers are capped for the large-grid variant, where 68 instead of 64 would cost the fourth resident
 // block per SM (measured: the output head at 88 us instead of 84 us); the others are left to the compiler.
-template <int MT, int EPI, int UB>
-__global__ void __launch_bounds__(SK_THREADS, (MT == 1 && UB == 0 && EPI != EPI_SWIGLU) ? 4 : 0)
+// NW: warps of a block, 8 or 16.  Sixteen split a long K inside one block (their sums meet in shared memory)
+// where eight would need a second block and the hand-over through global memory.
+template <int MT, int EPI, int UB, int NW = SK_WARPS>
+__global__ void __launch_bounds__(NW * 32, (MT == 1 && UB == 0 && EPI != EPI_SWIGLU) ? 4 : 0)
 skinny_gemm_kernel(const bf16* __restrict__ x, long ldx, const bf16* __restrict__ W, long ldw,
                    void* __restrict__ out, long ldo, int M, int N, int K, int I,
                    float* __restrict__ scratch, int* __restrict__ tickets) {
   constexpr int RT = (EPI == EPI_SWIGLU) ? 2 : 1;
-  __shared__ float red[SK_WARPS][RT * MT * 4 * 32];
+  __shared__ float red[NW][RT * MT * 4 * 32];
   __shared__ int is_last;
   const int ks = gridDim.x;                        // blocks that share these rows and split K
   const int krank = blockIdx.x;
@@ -114,11 +116,11 @@ skinny_gemm_kernel(const bf16* __restrict__ x, long ldx, const bf16* __restrict_
   // kernel waits for its predecessor (whose output is x), so the wait overlaps the memory latency.
   bool waited = false;
   // whole rounds: every load is issued before the first product, no predicates
-  for (; kb + (UNROLL - 1) * SK_WARPS < full_blocks; kb += SK_WARPS * UNROLL) {
+  for (; kb + (UNROLL - 1) * NW < full_blocks; kb += NW * UNROLL) {
     uint4 wa[UNROLL][RT][2], xb[UNROLL][MT];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
-      const int k = (kb + u * SK_WARPS) * 32 + c * 8;
+      const int k = (kb + u * NW) * 32 + c * 8;
 #pragma unroll
       for (int r = 0; r < RT; ++r)
 #pragma unroll
@@ -127,7 +129,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, long ldx, const bf16* __restrict_
     if (!waited) { pdl_wait(); waited = true; }
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
-      const int k = (kb + u * SK_WARPS) * 32 + c * 8;
+      const int k = (kb + u * NW) * 32 + c * 8;
 #pragma unroll
       for (int t = 0; t < MT; ++t)
         xb[u][t] = UB ? ld_plain16(xrow[t] + k) : __ldg(reinterpret_cast<const uint4*>(xrow[t] + k));
@@ -143,7 +145,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, long ldx, const bf16* __restrict_
         }
   }
   // what is left of this warp's blocks, one at a time; the last block of K may be partial
-  for (; kb < nblocks; kb += SK_WARPS) {
+  for (; kb < nblocks; kb += NW) {
     const int k = kb * 32 + c * 8;
     const bool ok = k < K;                               // K is a multiple of 8
     uint4 wa[RT][2], xb[MT];
@@ -181,10 +183,10 @@ skinny_gemm_kernel(const bf16* __restrict__ x, long ldx, const bf16* __restrict_
   constexpr int PER = MT * 4 * 32;
   float* shares = scratch + (size_t)blockIdx.y * ks * (RT * PER);
   if (ks > 1) {
-    for (int e = threadIdx.x; e < RT * PER; e += SK_THREADS) {
+    for (int e = threadIdx.x; e < RT * PER; e += (NW * 32)) {
       float v = 0.f;
 #pragma unroll
-      for (int w = 0; w < SK_WARPS; ++w) v += red[w][e];
+      for (int w = 0; w < NW; ++w) v += red[w][e];
       __stcg(shares + (size_t)krank * (RT * PER) + e, v);
     }
     __threadfence();
@@ -195,7 +197,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, long ldx, const bf16* __restrict_
     __threadfence();
     if (threadIdx.x == 0) tickets[blockIdx.y] = 0;  // ready for the next launch
   }
-  for (int e = threadIdx.x; e < PER; e += SK_THREADS) {
+  for (int e = threadIdx.x; e < PER; e += (NW * 32)) {
     const int ln = e & 31, i = (e >> 5) & 3, t = e >> 7;
     float v0 = 0.f, v1 = 0.f;
     if (ks > 1) {
@@ -205,7 +207,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, long ldx, const bf16* __restrict_
       }
     } else {
 #pragma unroll
-      for (int w = 0; w < SK_WARPS; ++w) {
+      for (int w = 0; w < NW; ++w) {
         v0 += red[w][e];
         if (RT == 2) v1 += red[w][PER + e];
       }
@@ -239,7 +241,10 @@ static int skinny_launch(const void* x, long ldx, const void* W, long ldw, void*
   const int unroll = ((rt * mt_pad <= 2) ? 4 : (rt * mt_pad <= 4 ? 2 : 1)) * ((small_grid && rt * mt_pad <= 1) ? 2 : 1);
   // split K over blocks only where a warp would need more than two rounds of loads and the grid is
   // small: the hand-over through global memory costs about as much as one round
-  const int per_warp = ((K + 31) / 32 + SK_WARPS - 1) / SK_WARPS;
+  // one block per SM or fewer and a long K: sixteen warps per block share K
+  const bool wide = mt <= 1 && small_grid && EPI != EPI_SWIGLU && row_blocks <= 148 && K >= 4096;
+  const int warps = wide ? 16 : SK_WARPS;
+  const int per_warp = ((K + 31) / 32 + warps - 1) / warps;
   int ks = 1;
   while (ks < 8 && per_warp > 2 * unroll * ks && row_blocks * ks < 4 * 148) ks *= 2;
   if (scratch == nullptr || tickets == nullptr || row_blocks > num_tickets) ks = 1;
@@ -251,7 +256,10 @@ static int skinny_launch(const void* x, long ldx, const void* W, long ldw, void*
   (skinny_gemm_kernel<MT_, EPI, 0><<<grid, SK_THREADS, 0, stream>>>((const bf16*)x, ldx, (const bf16*)W, ldw, \
                                                                     out, ldo, M, N, K, I, scratch, tickets), \
    st = launch_status())
-  if (mt <= 1 && small_grid && EPI != EPI_SWIGLU)
+  if (wide)
+    st = launch_pdl(skinny_gemm_kernel<1, EPI, 1, 16>, grid, dim3(16 * 32), 0, stream, (const bf16*)x, ldx,
+                    (const bf16*)W, ldw, out, ldo, M, N, K, I, scratch, tickets);
+  else if (mt <= 1 && small_grid && EPI != EPI_SWIGLU)
     st = launch_pdl(skinny_gemm_kernel<1, EPI, 1>, grid, dim3(SK_THREADS), 0, stream, (const bf16*)x, ldx,
                     (const bf16*)W, ldw, out, ldo, M, N, K, I, scratch, tickets);
   else if (mt <= 1) SK_GO(1);
