@@ -220,6 +220,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
   }
   // ---------------- teardown: both blocks meet, then the allocating warps free the tensor memory
+  if (*abort_flag) {
+    // copies this block issued may still be writing its shared memory (their barrier is in block 0, where this
+    // block cannot wait): give them 200,000 cycles, far more than a copy takes
+    const long long t0 = clock64();
+    while (clock64() - t0 < 200000) {}
+  }
   tc_fence_before();
   __syncthreads();
   t2_cluster_sync();
