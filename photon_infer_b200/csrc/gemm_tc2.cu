@@ -43,6 +43,19 @@
 #define T2_EPI_BF16 0
 #define T2_EPI_F32 1
 #define T2_EPI_SWIGLU 2
+#define T2_EPI_QKV 3                  // rows of q | k | v: q and k rotated, q to `out`, k and v into the paged cache
+
+// What the QKV epilogue needs beside the product (formulas: include/photon/ops/kernels/rope_kernel.hpp:54-84 for
+// the rotation of neighbouring pairs, src/ops/kernels/cuda/paged_kv_write.cu:26-77 for the cache write).
+struct T2Qkv {
+  const int* positions;               // [M]
+  const int* slot_mapping;            // [M] slot of the token in the paged cache, -1: not stored
+  const float* inv_freq;              // [d / 2]
+  const float2* table;                // (cos, sin) [table_positions, d / 2] or null
+  bf16* k_cache; bf16* v_cache;       // [pages, n_kv, page_size, d]
+  int table_positions, n_q, n_kv, d, page_size;
+  long num_slots;
+};
 
 __device__ __forceinline__ bool t2_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   const long long t0 = clock64();
@@ -85,7 +98,8 @@ __device__ __forceinline__ void t2_arrive_block0(uint64_t* bar) {
 template <int EPI>
 __global__ void __launch_bounds__(T2_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                void* __restrict__ out, long ldo, int M, int N, int K, int I, int tiles_n, int num_tiles, int* err) {
+                void* __restrict__ out, long ldo, int M, int N, int K, int I, int tiles_n, int num_tiles, int* err,
+                const T2Qkv Q) {
   extern __shared__ unsigned char t2_dyn[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)t2_dyn + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + T2_STAGES * T2_STAGE_BYTES);
@@ -177,6 +191,22 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const int m0 = (tile / tiles_n) * (2 * T2_BM) + (int)rank * T2_BM, n0 = (tile % tiles_n) * TILE_COLS;
       const int row = m0 + quad * 32 + lane;
       const uint32_t lane_addr = tmem_base + buf * T2_BN + ((uint32_t)(quad * 32) << 16);
+      // QKV epilogue: the token's position and its place in the cache, once per tile
+      int pos = 0;
+      long cache_row = -1;                          // (page * n_kv) * page_size + offset in the page, or -1
+      if (EPI == T2_EPI_QKV && row < M) {
+        pos = Q.positions[row];
+        const long slot = Q.slot_mapping[row];
+        if (slot >= Q.num_slots || slot < -1) report_error(err, PHOTON_DEV_BAD_SLOT, row, (int)slot, (int)Q.num_slots);
+        else if (slot >= 0) {
+          const long page = slot / Q.page_size;
+          cache_row = page * Q.n_kv * Q.page_size + (slot - page * Q.page_size);
+        }
+      }
+      // (cos, sin) of the token's 16 pairs at head offsets j0 = 0 and 32 (mod 64): with heads of 64 every other
+      // chunk of a tile asks for the same 16, so they are fetched once per tile, 16 bytes at a time
+      float4 rot_a[8], rot_b[8];
+      int rot_a_j0 = -1, rot_b_j0 = -1;
 #pragma unroll 1
       for (int c = 0; c < TILE_COLS; c += 32) {
         uint32_t v[32], u[32];
@@ -184,7 +214,66 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (EPI == T2_EPI_SWIGLU) tc_ld32(lane_addr + T2_BN / 2 + c, u);
         if (row < M) {
           const int col0 = n0 + c;
-          if (EPI == T2_EPI_F32) {
+          if (EPI == T2_EPI_QKV) {
+            if (col0 < N) {                           // N is a multiple of 32 here: the chunk is inside one head
+              const int qd = Q.n_q * Q.d, kd = Q.n_kv * Q.d, half = Q.d >> 1;
+              const int which = col0 < qd ? 0 : (col0 < qd + kd ? 1 : 2);
+              const int local = col0 - (which == 0 ? 0 : (which == 1 ? qd : qd + kd));
+              const int h = local / Q.d, j0 = local - h * Q.d;
+              float y[32];
+              if (which < 2) {
+                // two sets of registers, chosen by a branch (indexing them would put them in local memory)
+                auto rotate = [&](float4 (&rot)[8], int& have_j0) {
+                  if (have_j0 != j0) {
+                    have_j0 = j0;
+                    if (Q.table != nullptr && pos < Q.table_positions) {
+                      const float4* trow = reinterpret_cast<const float4*>(Q.table + (size_t)pos * half + (j0 >> 1));
+#pragma unroll
+                      for (int i = 0; i < 8; ++i) rot[i] = trow[i];           // 16-byte aligned: j0 is a multiple of 32
+                    } else {
+#pragma unroll
+                      for (int i = 0; i < 8; ++i) {
+                        float4 t4;
+                        sincosf((float)pos * Q.inv_freq[(j0 >> 1) + 2 * i], &t4.y, &t4.x);
+                        sincosf((float)pos * Q.inv_freq[(j0 >> 1) + 2 * i + 1], &t4.w, &t4.z);
+                        rot[i] = t4;
+                      }
+                    }
+                  }
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    const float4 t4 = rot[i];                                 // (cos, sin) of two pairs
+                    const float a0 = __uint_as_float(v[4 * i]), a1 = __uint_as_float(v[4 * i + 1]);
+                    const float b0 = __uint_as_float(v[4 * i + 2]), b1 = __uint_as_float(v[4 * i + 3]);
+                    y[4 * i] = a0 * t4.x - a1 * t4.y;
+                    y[4 * i + 1] = a0 * t4.y + a1 * t4.x;
+                    y[4 * i + 2] = b0 * t4.z - b1 * t4.w;
+                    y[4 * i + 3] = b0 * t4.w + b1 * t4.z;
+                  }
+                };
+                if ((j0 >> 5) & 1) rotate(rot_b, rot_b_j0);
+                else rotate(rot_a, rot_a_j0);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(v[j]);
+              }
+              bf16* dst = nullptr;
+              if (which == 0) dst = (bf16*)out + (size_t)row * ldo + col0;
+              else if (cache_row >= 0)
+                dst = (which == 1 ? Q.k_cache : Q.v_cache) + ((size_t)cache_row + (size_t)h * Q.page_size) * Q.d + j0;
+              if (dst != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  uint4 pk;
+                  __nv_bfloat162 p0 = __floats2bfloat162_rn(y[j], y[j + 1]), p1 = __floats2bfloat162_rn(y[j + 2], y[j + 3]);
+                  __nv_bfloat162 p2 = __floats2bfloat162_rn(y[j + 4], y[j + 5]), p3 = __floats2bfloat162_rn(y[j + 6], y[j + 7]);
+                  pk.x = *reinterpret_cast<uint32_t*>(&p0); pk.y = *reinterpret_cast<uint32_t*>(&p1);
+                  pk.z = *reinterpret_cast<uint32_t*>(&p2); pk.w = *reinterpret_cast<uint32_t*>(&p3);
+                  *reinterpret_cast<uint4*>(dst + j) = pk;
+                }
+              }
+            }
+          } else if (EPI == T2_EPI_F32) {
             float* dst = (float*)out + (size_t)row * ldo + col0;
 #pragma unroll
             for (int j = 0; j < 32; ++j) if (col0 + j < ncols) dst[j] = __uint_as_float(v[j]);
@@ -237,14 +326,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 }
 
 // ---------------------------------------------------------------- host side
-// epilogue: 0 bfloat16, 1 float, 2 SwiGLU (W holds 2I rows, out is [M, I]).  Same requirements as photon_gemm_tc.
-PHOTON_API int photon_gemm_tc2(const void* x, long ldx, const void* W, long ldw, void* out, long ldo, int M, int N,
-                               int K, int epilogue, int* err, cudaStream_t stream) {
+static int t2_launch(const void* x, long ldx, const void* W, long ldw, void* out, long ldo, int M, int N, int K,
+                     int epilogue, const T2Qkv& Q, int* err, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ((uintptr_t)x & 15) || ((uintptr_t)W & 15))
     return PHOTON_ERR_UNSUPPORTED;
   if (epilogue == T2_EPI_SWIGLU && (N & 1)) return PHOTON_ERR_ARGUMENT;
-  if (epilogue < 0 || epilogue > 2) return PHOTON_ERR_ARGUMENT;
+  if (epilogue < 0 || epilogue > 3) return PHOTON_ERR_ARGUMENT;
   const int I = N / 2;
   CUtensorMap map_a, map_w;
   int st = make_map(&map_a, x, M, K, ldx, T2_BM);
@@ -266,12 +354,12 @@ PHOTON_API int photon_gemm_tc2(const void* x, long ldx, const void* W, long ldw,
   const int pairs = num_tiles < num_sms / 2 ? num_tiles : num_sms / 2;
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e0 = cudaFuncSetAttribute(gemm_tc2_kernel<T2_EPI_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES);
-    cudaError_t e1 = cudaFuncSetAttribute(gemm_tc2_kernel<T2_EPI_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES);
-    cudaError_t e2 = cudaFuncSetAttribute(gemm_tc2_kernel<T2_EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES);
-    if (e0 != cudaSuccess) return (int)e0;
-    if (e1 != cudaSuccess) return (int)e1;
-    if (e2 != cudaSuccess) return (int)e2;
+    cudaError_t e[4];
+    e[0] = cudaFuncSetAttribute(gemm_tc2_kernel<T2_EPI_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES);
+    e[1] = cudaFuncSetAttribute(gemm_tc2_kernel<T2_EPI_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES);
+    e[2] = cudaFuncSetAttribute(gemm_tc2_kernel<T2_EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES);
+    e[3] = cudaFuncSetAttribute(gemm_tc2_kernel<T2_EPI_QKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES);
+    for (int i = 0; i < 4; ++i) if (e[i] != cudaSuccess) return (int)e[i];
     attr_done = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -284,11 +372,45 @@ PHOTON_API int photon_gemm_tc2(const void* x, long ldx, const void* W, long ldw,
   cfg.attrs = attr;
   cfg.numAttrs = photon_pdl_enabled(stream) ? 2 : 1;
   cudaError_t e;
+#define T2_GO(EPI_) cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<EPI_>, map_a, map_w, out, ldo, M, N, K, I, tiles_n, num_tiles, err, Q)
   switch (epilogue) {
-    case T2_EPI_BF16: e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<T2_EPI_BF16>, map_a, map_w, out, ldo, M, N, K, I, tiles_n, num_tiles, err); break;
-    case T2_EPI_F32: e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<T2_EPI_F32>, map_a, map_w, out, ldo, M, N, K, I, tiles_n, num_tiles, err); break;
-    default: e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<T2_EPI_SWIGLU>, map_a, map_w, out, ldo, M, N, K, I, tiles_n, num_tiles, err); break;
+    case T2_EPI_BF16: e = T2_GO(T2_EPI_BF16); break;
+    case T2_EPI_F32: e = T2_GO(T2_EPI_F32); break;
+    case T2_EPI_SWIGLU: e = T2_GO(T2_EPI_SWIGLU); break;
+    default: e = T2_GO(T2_EPI_QKV); break;
   }
+#undef T2_GO
   if (e != cudaSuccess) return (int)e;
   return launch_status();
+}
+
+// epilogue: 0 bfloat16, 1 float, 2 SwiGLU (W holds 2I rows, out is [M, I]).  Same requirements as photon_gemm_tc.
+PHOTON_API int photon_gemm_tc2(const void* x, long ldx, const void* W, long ldw, void* out, long ldo, int M, int N,
+                               int K, int epilogue, int* err, cudaStream_t stream) {
+  if (epilogue < 0 || epilogue > 2) return PHOTON_ERR_ARGUMENT;
+  T2Qkv Q = {};
+  return t2_launch(x, ldx, W, ldw, out, ldo, M, N, K, epilogue, Q, err, stream);
+}
+
+// The q/k/v product of a step with rotation and cache write in the epilogue: W [(n_q + 2 n_kv) d, K] holds the
+// rows of q, then k, then v, rotation partners of q and k as neighbours; q_out [M, n_q d] gets the rotated
+// queries, the rotated keys and the values go to slot_mapping[row] of the paged cache ([pages, n_kv, page_size,
+// d]; slot -1: not stored).  d must be a multiple of 32.  table (may be null): (cos, sin) for positions below
+// table_positions, else they are computed in place.
+PHOTON_API int photon_gemm_tc2_qkv(const void* x, long ldx, const void* W, long ldw, void* q_out, long ldo, int M,
+                                   int K, const int* positions, const int* slot_mapping, const float* inv_freq,
+                                   const void* table, int table_positions, void* k_cache, void* v_cache, int n_q,
+                                   int n_kv, int d, int page_size, long num_slots, int* err, cudaStream_t stream) {
+  if (n_q <= 0 || n_kv <= 0 || d <= 0 || (d & 31) || page_size <= 0) return PHOTON_ERR_UNSUPPORTED;
+  if (positions == nullptr || slot_mapping == nullptr || inv_freq == nullptr || k_cache == nullptr || v_cache == nullptr)
+    return PHOTON_ERR_ARGUMENT;
+  if (((uintptr_t)q_out & 15) || (ldo & 7) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15)) return PHOTON_ERR_ARGUMENT;
+  T2Qkv Q;
+  Q.positions = positions; Q.slot_mapping = slot_mapping; Q.inv_freq = inv_freq; Q.table = (const float2*)table;
+  Q.table_positions = table != nullptr ? table_positions : 0;
+  Q.k_cache = (bf16*)k_cache; Q.v_cache = (bf16*)v_cache; Q.n_q = n_q; Q.n_kv = n_kv; Q.d = d; Q.page_size = page_size;
+  Q.num_slots = num_slots;
+  const long N = (long)(n_q + 2 * n_kv) * d;
+  if (N > 0x7fffffff) return PHOTON_ERR_UNSUPPORTED;
+  return t2_launch(x, ldx, W, ldw, q_out, ldo, M, (int)N, K, T2_EPI_QKV, Q, err, stream);
 }

@@ -192,3 +192,23 @@ PHOTON_API int photon_rope_kv_write(void* q, long q_stride, void* k, long k_stri
         rotate, write_kv, err);
   return launch_status();
 }
+
+// Table of (cos, sin) of position * inv_freq[j] for positions 0 .. count - 1: the same expression, in the same
+// 32-bit arithmetic, that the kernels above evaluate in place, so a kernel that reads the table rotates
+// exactly as they do.  out: float2 [count, half].
+__global__ void rope_table_kernel(const float* __restrict__ inv_freq, int half, long total, float2* __restrict__ out) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long p = i / half;
+  const int j = (int)(i - p * half);
+  float sn, cs;
+  sincosf((float)p * inv_freq[j], &sn, &cs);
+  out[i] = make_float2(cs, sn);
+}
+
+PHOTON_API int photon_rope_table(const float* inv_freq, int half, int count, void* out, cudaStream_t stream) {
+  if (half <= 0 || count <= 0) return 0;
+  const long total = (long)half * count;
+  rope_table_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(inv_freq, half, total, (float2*)out);
+  return launch_status();
+}

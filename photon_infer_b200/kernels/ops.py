@@ -518,6 +518,67 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: 
              _ptr(err), _stream()), module)
 
 
+def rope_table(inv_freq: torch.Tensor, count: int) -> torch.Tensor:
+    """``(cos, sin)`` of ``position * inv_freq[j]`` for positions below ``count``, float32
+    ``[count, len(inv_freq), 2]``, computed on the device with the expression the rotary kernels use."""
+    _cuda(inv_freq)
+    if inv_freq.dtype != torch.float32 or not inv_freq.is_contiguous():
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "rope_table: inv_freq must be contiguous float32")
+    half = inv_freq.numel()
+    out = torch.empty((int(count), half, 2), dtype=torch.float32, device=inv_freq.device)
+    f = _fn("rope_kv", "photon_rope_table", [c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(inv_freq), half, int(count), _ptr(out), _stream()), "rope_table")
+    return out
+
+
+def gemm_tc_qkv_supported(x: torch.Tensor, w_qkv: torch.Tensor, head_dim: int) -> bool:
+    """The q/k/v product with rotation and cache write in its epilogue: the tcgen05 kernel on pairs of SMs with
+    enough tiles, heads that are a multiple of 32 wide."""
+    M = x.shape[0]
+    return (gemm_tc_supported(x, w_qkv) and M >= TC_PAIR_MIN_ROWS and head_dim % 32 == 0
+            and gemm_tc_tiles(M, w_qkv.shape[0]) >= TC_MIN_TILES)
+
+
+def gemm_tc_qkv(x: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor,
+                slot_mapping: torch.Tensor, inv_freq: torch.Tensor, table: Optional[torch.Tensor],
+                k_cache: torch.Tensor, v_cache: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
+                err: Optional[torch.Tensor] = None) -> None:
+    """``x @ w_qkv^T`` (rows of q, then k, then v; rotation partners of q and k as neighbours) with the
+    rotation and the cache write in the epilogue: rotated queries to ``q_out [M, n_q * d]``, rotated keys and
+    the values to ``slot_mapping`` of the paged cache ``[pages, n_kv, page_size, d]``.  ``table``: from
+    ``rope_table`` (positions beyond it are computed in place)."""
+    _cuda(x, w_qkv, q_out, positions, slot_mapping, inv_freq, table, k_cache, v_cache, err)
+    M, K = x.shape
+    if not gemm_tc_supported(x, w_qkv) or w_qkv.shape != ((n_q + 2 * n_kv) * head_dim, K) or head_dim % 32:
+        raise PhotonError(ErrorCode.UNSUPPORTED_SIZE, "gemm_tc_qkv: needs bfloat16, K a multiple of 8, aligned rows, "
+                          "head_dim a multiple of 32 and a weight of (n_q + 2 n_kv) * head_dim rows")
+    if q_out.shape != (M, n_q * head_dim) or q_out.dtype != torch.bfloat16 or q_out.stride(1) != 1:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, f"gemm_tc_qkv: q_out must be bfloat16 [{M}, {n_q * head_dim}]")
+    for name, t in (("positions", positions), ("slot_mapping", slot_mapping)):
+        _int32(t, name)
+        if t.numel() < M:
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, f"gemm_tc_qkv: {name} must have an entry per row")
+    if k_cache.dtype != torch.bfloat16 or v_cache.dtype != torch.bfloat16 or not k_cache.is_contiguous() \
+            or not v_cache.is_contiguous() or k_cache.shape != v_cache.shape or k_cache.shape[1] != n_kv \
+            or k_cache.shape[3] != head_dim:
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "gemm_tc_qkv: the caches must be contiguous bfloat16 [pages, n_kv, page, d]")
+    if inv_freq.dtype != torch.float32 or inv_freq.numel() != head_dim // 2:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "gemm_tc_qkv: inv_freq must be float32 [head_dim / 2]")
+    count = 0
+    if table is not None:
+        if table.dtype != torch.float32 or table.dim() != 3 or table.shape[1:] != (head_dim // 2, 2) or not table.is_contiguous():
+            raise PhotonError(ErrorCode.SHAPE_MISMATCH, "gemm_tc_qkv: table must be float32 [positions, head_dim / 2, 2]")
+        count = table.shape[0]
+    f = _fn("gemm_tc2", "photon_gemm_tc2_qkv",
+            [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_long, c_void_p, c_void_p])
+    if err is None:
+        err = _error_word(x.device)
+    _check(f(_ptr(x), x.stride(0), _ptr(w_qkv), w_qkv.stride(0), _ptr(q_out), q_out.stride(0), M, K, _ptr(positions),
+             _ptr(slot_mapping), _ptr(inv_freq), _ptr(table), count, _ptr(k_cache), _ptr(v_cache), n_q, n_kv, head_dim,
+             k_cache.shape[2], k_cache.shape[0] * k_cache.shape[2], _ptr(err), _stream()), "gemm_tc_qkv")
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """``x [M, K] @ weight[N, K]^T``.  float32: this package's FMA kernel (true 32-bit).

@@ -106,6 +106,16 @@ class PagedAttention(Mixer):
         T = h.shape[0]
         d = self.head_dim
         group = ctx.groups[cache.group]
+        pe = self.position_encoding
+        if (not cache.shared and cache.k is not None and isinstance(pe, RotaryEncoding) and self.pairs_adjacent
+                and h.dtype == torch.bfloat16 and ops.gemm_tc_qkv_supported(h, self.w_qkv, d)):
+            # a long prompt portion: rotation and cache write ride in the epilogue of the q/k/v product
+            q = torch.empty((T, self.n_q * d), dtype=h.dtype, device=h.device)
+            ops.gemm_tc_qkv(h, self.w_qkv, q, ctx.positions, group.slot_mapping, pe.inv_freq,
+                            pe.table(ctx.max_context_len), cache.k, cache.v, self.n_q, self.n_kv, d, ctx.error_flag)
+            attn = torch.empty((T, self.n_q * d), dtype=h.dtype, device=h.device)
+            self.attend(q, attn, ctx, cache)
+            return project(attn, self.w_o)
         if cache.shared:
             # keys and values come from another entry's pages: only the queries are computed
             q = project(h, self.w_qkv[: self.n_q * d])

@@ -56,9 +56,21 @@ class RotaryEncoding(PositionEncoding):
         self.interleaved = bool(interleaved)
         self.inv_freq_host = inverse_frequencies(head_dim, self.theta, self.scaling)
         self.inv_freq: Optional[torch.Tensor] = None
+        self._table: Optional[torch.Tensor] = None
 
     def to_device(self, device) -> None:
         self.inv_freq = self.inv_freq_host.to(device)
+        self._table = None
+
+    def table(self, positions: int) -> torch.Tensor:
+        """``(cos, sin)`` for positions below a power of two that covers ``positions`` (grown on demand,
+        built on the device with the kernels' own expression): for kernels that look angles up."""
+        if getattr(self, "_table", None) is None or self._table.shape[0] < positions:
+            count = 1024
+            while count < positions:
+                count *= 2
+            self._table = ops.rope_table(self.inv_freq, count)
+        return self._table
 
     def apply(self, q, k, positions) -> None:
         """In place; ``q [T, n_q, d]`` and ``k [T, n_kv, d]`` may be views with any row stride."""

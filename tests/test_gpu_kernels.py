@@ -712,3 +712,52 @@ def test_gemm_tcgen05_pairs_of_sms(M, N, K):
         assert err.cpu().tolist()[0] == 0
         g, u = want[:, :I], want[:, I:]
         _close(act, g / (1 + torch.exp(-g)) * u, torch.bfloat16)
+
+
+@pytest.mark.parametrize("M,n_q,n_kv,d,K,ps,use_table", [(300, 4, 2, 64, 128, 16, True), (513, 6, 2, 32, 72, 8, False),
+                                                         (2048, 32, 8, 64, 2048, 16, True), (260, 3, 1, 128, 64, 32, True)])
+def test_gemm_tcgen05_qkv_epilogue(M, n_q, n_kv, d, K, ps, use_table):
+    """The q/k/v product with rotation and cache write in its epilogue against float64: rotated queries in
+    q_out, rotated keys and plain values at their slots of the paged cache, other slots untouched."""
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(33)
+    N = (n_q + 2 * n_kv) * d
+    x = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).bfloat16()
+    inv_freq = (10000.0 ** (-torch.arange(0, d, 2, dtype=torch.float64) / d)).float().to(DEV)
+    positions = (torch.arange(M, dtype=torch.int32) + 37).to(DEV)
+    pages = (M + ps - 1) // ps + 2
+    slots = torch.randperm(pages * ps)[:M].to(torch.int32)
+    slots[5] = -1                                               # a token that is not stored
+    kc = torch.full((pages, n_kv, ps, d), 7.0, dtype=torch.bfloat16, device=DEV)
+    vc = torch.full_like(kc, 7.0)
+    q_out = torch.full((M, n_q * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    table = ops.rope_table(inv_freq, 256) if use_table else None     # shorter than the positions: both paths run
+    ops.gemm_tc_qkv(x, w, q_out, positions, slots.to(DEV), inv_freq, table, kc, vc, n_q, n_kv, d, err)
+    assert err.cpu().tolist()[0] == 0
+    y = (x.double() @ w.double().t()).cpu()
+    ang = positions.cpu().double()[:, None] * inv_freq.cpu().double()[None, :]
+    cs, sn = torch.cos(ang), torch.sin(ang)
+
+    def rotate(t, heads):                                       # neighbouring pairs
+        t = t.reshape(M, heads, d // 2, 2)
+        a, b = t[..., 0], t[..., 1]
+        return torch.stack([a * cs[:, None] - b * sn[:, None], a * sn[:, None] + b * cs[:, None]], dim=-1).reshape(M, heads * d)
+    q_want = rotate(y[:, : n_q * d], n_q)
+    k_want = rotate(y[:, n_q * d: (n_q + n_kv) * d], n_kv).reshape(M, n_kv, d)
+    v_want = y[:, (n_q + n_kv) * d:].reshape(M, n_kv, d)
+    _close(q_out, q_want, torch.bfloat16)
+    kc_c, vc_c = kc.cpu().double(), vc.cpu().double()
+    written = torch.zeros(pages * ps, dtype=torch.bool)
+    scale_k, scale_v = float(k_want.abs().max()), float(v_want.abs().max())
+    for t in range(M):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        written[s] = True
+        assert float((kc_c[s // ps, :, s % ps] - k_want[t]).abs().max()) <= 6e-3 * scale_k
+        assert float((vc_c[s // ps, :, s % ps] - v_want[t]).abs().max()) <= 6e-3 * scale_v
+    untouched = ~written
+    assert bool((kc_c.permute(0, 2, 1, 3).reshape(pages * ps, -1)[untouched] == 7.0).all())
+    assert bool((vc_c.permute(0, 2, 1, 3).reshape(pages * ps, -1)[untouched] == 7.0).all())
