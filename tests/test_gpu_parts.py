@@ -281,3 +281,134 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     runner.cache.add_request("c")
     r = runner.step([StepEntry("c", b, list(range(27)))])
     assert rel_err(r.logits.cpu(), plain(b)) < 2e-5
+
+
+# --------------------------------------------------------------------------- a toy routed feed-forward and a toy position encoding
+
+def _toy_routed_ff():
+    """Top-1 of E small experts: router logits in 32-bit, probability of the chosen expert times
+    W2_e relu(W1_e h).  Plain torch ops; the framework only sees the FeedForward interface."""
+    from photon_infer_b200.parts.base import FeedForward, TensorSpec
+
+    class Top1Experts(FeedForward):
+        def __init__(self, hidden_size, inner_size, experts):
+            self.h, self.i, self.e = hidden_size, inner_size, experts
+            self.router = self.w1 = self.w2 = None
+
+        def tensor_specs(self):
+            return [TensorSpec("router.weight", (self.e, self.h)), TensorSpec("w1.weight", (self.e * self.i, self.h)),
+                    TensorSpec("w2.weight", (self.e * self.h, self.i))]
+
+        def load(self, tensors):
+            self.router = tensors["router.weight"]
+            self.w1 = tensors["w1.weight"].view(self.e, self.i, self.h)
+            self.w2 = tensors["w2.weight"].view(self.e, self.h, self.i)
+
+        def forward(self, h, ctx):
+            logits = h.float() @ self.router.float().t()                      # 32-bit router
+            prob = torch.softmax(logits, dim=-1)
+            top = prob.argmax(dim=-1)
+            out = torch.zeros_like(h)
+            for e in range(self.e):
+                rows = (top == e).nonzero().flatten()
+                if rows.numel():
+                    x = h[rows]
+                    y = torch.relu(x @ self.w1[e].t()) @ self.w2[e].t()
+                    out[rows] = (y.float() * prob[rows, e][:, None]).to(h.dtype)
+            return out
+
+    return Top1Experts
+
+
+def _toy_position_encoding():
+    """Queries and keys shrink with their position: x <- x / (1 + rate * pos).  No tensors."""
+    from photon_infer_b200.parts.base import PositionEncoding
+
+    class DecayEncoding(PositionEncoding):
+        def __init__(self, rate):
+            self.rate = float(rate)
+
+        def apply(self, q, k, positions):
+            s = 1.0 / (1.0 + self.rate * positions.float())
+            q.mul_(s[:, None, None].to(q.dtype))
+            if k is not None:
+                k.mul_(s[:, None, None].to(k.dtype))
+
+    return DecayEncoding
+
+
+def test_toy_routed_feed_forward_and_position_encoding_without_touching_the_framework(tmp_path):
+    """An architecture whose layers use the framework's paged attention with a position encoding defined
+    here, and a routed feed-forward defined here: registered, given random weights, loaded and stepped in
+    portions beside another request, against the same model written out with the plain functions."""
+    from photon_infer_b200.config import EngineOptions, LlamaConfig, register_architecture
+    from photon_infer_b200.engine.loading import build_runner
+    from photon_infer_b200.engine.runner import StepEntry
+    from photon_infer_b200.models.llama import build_llama_spec
+    from photon_infer_b200.models.spec import PartSpec
+    from photon_infer_b200.parts.registry import register_feed_forward, register_position_encoding
+    from photon_infer_b200.weights import write_random_model
+    from plain.llama_plain import causal_attention, feed_forward, linear, rms_norm
+    from safetensors.torch import load_file
+
+    E, INNER, RATE = 3, 40, 0.03
+    register_feed_forward("top1_experts_for_test", _toy_routed_ff(), replace=True)
+    register_position_encoding("decay_for_test", _toy_position_encoding(), replace=True)
+
+    def build(cfg):
+        spec = build_llama_spec(cfg)
+        spec.position_encodings = {"decay": PartSpec("decay_for_test", {"rate": RATE})}
+        for i, layer in enumerate(spec.layers):
+            layer.mixer.params["position_encoding"] = "decay"
+            if i == 1:                                                         # the middle layer routes
+                layer.feed_forward = PartSpec("top1_experts_for_test",
+                                              {"hidden_size": cfg.hidden_size, "inner_size": INNER, "experts": E}, "moe.")
+        return spec
+    register_architecture("ToyRoutedModelForTest", LlamaConfig, build, replace=True)
+
+    cfg = dict(TINY["tiny_b"]["config"], architectures=["ToyRoutedModelForTest"], num_hidden_layers=3)
+    folder = str(tmp_path)
+    names = write_random_model(folder, cfg, seed=12, init_std=0.08, norm_std=0.1)
+    assert "model.layers.1.moe.router.weight" in names and "model.layers.1.mlp.gate_proj.weight" not in names
+    assert "model.layers.0.mlp.gate_proj.weight" in names
+    runner = build_runner(folder, EngineOptions(dtype="float32", block_size=8, max_cache_tokens=256, max_sequences=3))
+
+    w = {k: v.float() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    c = LlamaConfig.from_dict(cfg)
+    n_q, n_kv, d = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+
+    def plain(ids):
+        T = len(ids)
+        x = w["model.embed_tokens.weight"][torch.tensor(ids)]
+        s = (1.0 / (1.0 + RATE * torch.arange(T).float()))[:, None, None]
+        for l in range(3):
+            p = f"model.layers.{l}."
+            h = rms_norm(x, w[p + "input_layernorm.weight"], c.rms_norm_eps)
+            q = linear(h, w[p + "self_attn.q_proj.weight"]).view(T, n_q, d) * s
+            k = linear(h, w[p + "self_attn.k_proj.weight"]).view(T, n_kv, d) * s
+            v = linear(h, w[p + "self_attn.v_proj.weight"]).view(T, n_kv, d)
+            x = x + linear(causal_attention(q, k, v).reshape(T, -1), w[p + "self_attn.o_proj.weight"])
+            h2 = rms_norm(x, w[p + "post_attention_layernorm.weight"], c.rms_norm_eps)
+            if l == 1:
+                prob = torch.softmax(h2 @ w[p + "moe.router.weight"].t(), dim=-1)
+                top = prob.argmax(dim=-1)
+                w1 = w[p + "moe.w1.weight"].view(E, INNER, -1)
+                w2 = w[p + "moe.w2.weight"].view(E, -1, INNER)
+                y = torch.stack([torch.relu(h2[t] @ w1[top[t]].t()) @ w2[top[t]].t() * prob[t, top[t]] for t in range(T)])
+                x = x + y
+            else:
+                x = x + feed_forward(h2, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+        return linear(rms_norm(x, w["model.norm.weight"], c.rms_norm_eps), w["lm_head.weight"])
+
+    vocab = cfg["vocab_size"]
+    a, b = random_ids(37, vocab, seed=3), random_ids(21, vocab, seed=4)
+    runner.cache.add_request("a"); runner.cache.add_request("b")
+    got_a, got_b = [], []
+    r = runner.step([StepEntry("a", a[:20], list(range(20))), StepEntry("b", b[:2], [0, 1])])
+    got_a.append(r.logits[:20].cpu()); got_b.append(r.logits[20:].cpu())
+    r = runner.step([StepEntry("b", b[2:], list(range(19))), StepEntry("a", a[20:21], [0])])
+    got_b.append(r.logits[:19].cpu()); got_a.append(r.logits[19:].cpu())
+    r = runner.step([StepEntry("a", a[21:], list(range(16)))])
+    got_a.append(r.logits.cpu())
+    assert rel_err(torch.cat(got_a), plain(a)) < 2e-5
+    assert rel_err(torch.cat(got_b), plain(b)) < 2e-5
