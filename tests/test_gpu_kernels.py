@@ -688,7 +688,7 @@ def test_attention_tcgen05_refuses_other_sizes():
 
 
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (1, 8, 8), (100, 300, 72), (257, 513, 520), (2048, 3072, 2048),
-                                   (333, 389, 120), (4096, 256, 8192), (129, 129, 136)])
+                                   (333, 389, 120), (4096, 256, 8192), (129, 129, 136), (2560, 2100, 136)])
 def test_gemm_tcgen05_pairs_of_sms(M, N, K):
     """The product on pairs of SMs (cta_group::2) against float64, with partial tiles on every side."""
     from photon_infer_b200.kernels import ops
