@@ -54,19 +54,6 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a, uint64_t b, 
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(bar)) : "memory");
 }
-// The same two, for a warp that runs the issuing code with all lanes in step: one elected lane
-// issues.  Addresses and descriptors then stay warp-uniform values, which is what the instruction
-// takes; inside an `if (lane == 0)` every operand has to be moved over one by one.
-__device__ __forceinline__ void tc_mma_elect(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n.reg .pred p, pe;\nelect.sync _|pe, 0xffffffff;\nsetp.ne.b32 p, %4, 0;\n"
-               "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-               ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_commit_elect(uint64_t* bar) {
-  asm volatile("{\n.reg .pred pe;\nelect.sync _|pe, 0xffffffff;\n"
-               "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}"
-               ::"r"(tc_smem(bar)) : "memory");
-}
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
