@@ -13,7 +13,6 @@ from __future__ import annotations
 
 import dataclasses
 import sys
-import time
 from typing import Dict, List, Optional, Sequence
 
 import torch

@@ -1,7 +1,6 @@
 """From a model folder to a model on the device with its cache and step function."""
 from __future__ import annotations
 
-import dataclasses
 from typing import Optional
 
 import torch

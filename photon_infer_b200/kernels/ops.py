@@ -7,8 +7,8 @@ correctly refuses it (``UNSUPPORTED_SIZE``) instead of giving a wrong result.
 """
 from __future__ import annotations
 
-import os
 import ctypes
+import os
 from ctypes import c_float, c_int, c_long, c_void_p
 from typing import Optional
 

@@ -17,7 +17,7 @@ from ..kernels import ops
 from ..parts.base import (Block, LayerCache, Mixer, PagedCacheSpec, Part, StateSpec, StepContext,
                           TensorSpec)
 from ..parts.registry import create_part
-from .spec import LayerSpec, ModelSpec, PartSpec
+from .spec import LayerSpec, ModelSpec
 
 
 def _build_position_encodings(spec: ModelSpec) -> Dict[str, Part]:

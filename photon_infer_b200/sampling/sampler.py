@@ -11,7 +11,7 @@ not depend on what else is in the batch.  The reference parses ``top_p`` and ign
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import Sequence
 
 import torch
 
