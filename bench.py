@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput of the engine at the Llama 3.2 1B shape, one GPU.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--workloads all|headline]
 
 Prints ONE JSON line.  A step is one decode step of ``--batch`` requests, each with a
 512-token prompt in the cache and up to 256 generated tokens.  ``value`` is decoded
@@ -9,8 +9,16 @@ tokens per second timed on the device; ``e2e`` is the same through the Python en
 point (``ContinuousBatchEngine.step``), token ids from the host in and sampled ids back
 every step.  The weights are random (seeded), the token ids synthetic.
 
-``--impl reference`` would run lumia431/photon_infer itself; it cannot be installed
-here (see the ``unavailable`` line it prints).
+Two more workloads go into ``points`` of the same line (``--workloads headline`` leaves them out):
+
+* ``llama3b_*``: the Llama 3.2 3B shape under continuous batching: 64 requests with prompts of 128 to
+  2,048 tokens and 256 generated tokens each, one request arriving per scheduler step, through
+  ``ContinuousBatchEngine.step`` (host ids in, sampled ids out);
+* ``llama8b_*``: the Llama 3.1 8B shape at long context: eight prompts of 16,384 tokens fed in portions
+  of 2,048, then 256 decode steps of all eight.
+
+``--impl reference`` runs lumia431/photon_infer itself where it could be built (``baseline/``); else it
+prints an ``unavailable`` line.
 """
 from __future__ import annotations
 
@@ -26,7 +34,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# The sizes of the Llama 3.2 1B shape (the third configuration of BASELINE.json).
+# The sizes of the Llama 3.2 1B shape: 16 layers, 2,048 wide, 32/8 heads of 64, vocabulary 128,256.
 LLAMA_1B = dict(
     architectures=["LlamaForCausalLM"], hidden_size=2048, intermediate_size=8192, num_hidden_layers=16,
     num_attention_heads=32, num_key_value_heads=8, head_dim=64, vocab_size=128256,
@@ -34,6 +42,9 @@ LLAMA_1B = dict(
     rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
                       original_max_position_embeddings=8192),
     tie_word_embeddings=True, bos_token_id=128000, eos_token_id=128001)
+LLAMA_3B = dict(LLAMA_1B, hidden_size=3072, num_hidden_layers=28, num_attention_heads=24, head_dim=128)
+LLAMA_8B = dict(LLAMA_1B, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32, head_dim=128,
+                rope_scaling=dict(LLAMA_1B["rope_scaling"], factor=8.0), tie_word_embeddings=False)
 PROMPT_LEN, GEN_LEN, CONTEXT, PREFILL_TOKENS = 512, 256, 4096, 2048
 PUBLISHED_BATCH8_TOK_S = 720.0       # the reference's README: batch 8, A100, INT8 weights
 
@@ -103,6 +114,199 @@ class ClockSampler:
             self.proc.terminate()
 
 
+def layer_flops_per_token(cfg) -> int:
+    """Multiply-adds x 2 of the products of one layer for one token (attention over the keys not included)."""
+    H, I, d = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
+    nq, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    return 2 * (H * (nq + 2 * nkv) * d + nq * d * H + 3 * H * I)
+
+
+def step_flops(cfg, layers, entries, wanted_rows) -> int:
+    """``entries``: (tokens in the step, tokens cached before) per request.  Products of every token, QK^T and
+    PV of every token over the keys it sees, the output head on the wanted rows."""
+    nq, d = cfg["num_attention_heads"], cfg["head_dim"]
+    tokens = sum(n for n, _ in entries)
+    keys = sum(n * c + n * (n + 1) // 2 for n, c in entries)
+    return layers * (tokens * layer_flops_per_token(cfg) + 4 * nq * d * keys) \
+        + 2 * cfg["hidden_size"] * cfg["vocab_size"] * wanted_rows
+
+
+def run_3b_continuous(args, hbm_peak, tf_peak):
+    """Continuous batching at the Llama 3.2 3B shape through the engine's entry point."""
+    import torch
+    from photon_infer_b200 import EngineOptions
+    from photon_infer_b200.engine.engine import ContinuousBatchEngine
+    from photon_infer_b200.engine.loading import build_runner, random_model
+
+    n_req, gen, lo, hi = 64, 256, 128, 2048
+    cfg = dict(LLAMA_3B, num_hidden_layers=args.layers_3b or LLAMA_3B["num_hidden_layers"])
+    layers = cfg["num_hidden_layers"]
+    model = random_model(cfg, args.dtype, seed=3)
+    options = EngineOptions(dtype=args.dtype, block_size=args.block_size, max_cache_tokens=n_req * (hi + gen + 16),
+                            max_sequences=n_req, max_batch_size=n_req, chunk_size=2048, max_num_batched_tokens=2048,
+                            max_model_len=CONTEXT, use_cuda_graphs=not args.no_graphs)
+    runner = build_runner(None, options, model=model)
+    cache = runner.cache
+    gen_rng = torch.Generator().manual_seed(33)
+    lengths = torch.randint(lo, hi + 1, (n_req,), generator=gen_rng).tolist()
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=gen_rng).tolist() for n in lengths]
+
+    log = []                                   # per launched step: (call index, [(tokens, cached before)], wanted rows)
+    call = [0]
+    real_step = runner.step
+
+    def logged_step(entries, **kw):
+        log.append((call[0], [(len(e.tokens), cache.length(e.request_id)) for e in entries],
+                    sum(len(e.want) for e in entries)))
+        return real_step(entries, **kw)
+    runner.step = logged_step
+
+    def one_pass(timed):
+        engine = ContinuousBatchEngine(None, options, runner=runner)
+        pending = list(prompts)
+        events = []
+        del log[:]
+        call[0] = 0
+        torch.cuda.synchronize()
+        start = torch.cuda.Event(enable_timing=True)
+        start.record()
+        t0 = time.perf_counter()
+        while pending or engine.has_work():
+            if pending:                         # one arrival per scheduler step
+                engine.add_request(pending.pop(0), max_new_tokens=gen, ignore_eos=True)
+            engine.step()
+            if timed:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                events.append(ev)
+            call[0] += 1
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        runner.check_device_errors()
+        done = sum(r.num_generated() for r in engine.scheduler.requests.values())
+        assert done == n_req * gen, (done, n_req * gen)
+        return wall, start, events, engine
+
+    one_pass(False)                             # modules, graphs of every batch size and table width
+    h2d0 = runner.h2d_bytes
+    wall, start, events, engine = one_pass(True)
+    # device time between the events of consecutive calls belongs to the step launched in the later call
+    ms = [(events[i - 1] if i else start).elapsed_time(events[i]) for i in range(len(events))]
+    weight_bytes = model.step_weight_bytes()
+    kv_per_token = cache.bytes_per_token()
+    dec_ms = dec_bytes = dec_steps = dec_tokens = 0
+    mix_ms = mix_flops = mix_steps = mix_tokens = 0
+    for idx, entries, wanted in log:
+        if all(n == 1 for n, _ in entries):
+            dec_ms += ms[idx]
+            dec_bytes += weight_bytes + kv_per_token * sum(c + 1 for _, c in entries)
+            dec_steps += 1
+            dec_tokens += len(entries)
+        else:
+            mix_ms += ms[idx]
+            mix_flops += step_flops(cfg, layers, entries, wanted)
+            mix_steps += 1
+            mix_tokens += sum(n for n, _ in entries)
+    total_ms = start.elapsed_time(events[-1])
+    stats = engine.get_stats()
+    out = {
+        "llama3b_continuous_tok_s": round(n_req * gen / wall, 1),
+        "llama3b_device_tok_s": round(n_req * gen / (total_ms / 1e3), 1),
+        "llama3b_steps": len(log),
+        "llama3b_decode_steps": dec_steps,
+        "llama3b_decode_ms_per_step": round(dec_ms / max(dec_steps, 1), 4),
+        "llama3b_decode_batch_mean": round(dec_tokens / max(dec_steps, 1), 1),
+        "llama3b_decode_hbm_frac": round(dec_bytes / max(dec_ms, 1e-9) / 1e6 / hbm_peak, 4),
+        "llama3b_mixed_steps": mix_steps,
+        "llama3b_mixed_tokens_per_step": round(mix_tokens / max(mix_steps, 1), 1),
+        "llama3b_mixed_ms_per_step": round(mix_ms / max(mix_steps, 1), 4),
+        "llama3b_mixed_tensor_frac": round(mix_flops / max(mix_ms, 1e-9) / 1e9 / tf_peak, 4),
+        "llama3b_h2d_bytes_per_step": (runner.h2d_bytes - h2d0) // max(len(log), 1),
+        "llama3b_preemptions": stats.preemptions,
+        "llama3b_layers": layers, "llama3b_layers_of_model": LLAMA_3B["num_hidden_layers"],
+    }
+    runner.step = real_step
+    del engine, runner, model
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_8b_long(args, hbm_peak, tf_peak):
+    """Long context at the Llama 3.1 8B shape: 16,384-token prompts in portions of 2,048, then decode."""
+    import torch
+    from photon_infer_b200 import EngineOptions
+    from photon_infer_b200.engine.loading import build_runner, random_model
+    from photon_infer_b200.engine.runner import StepEntry
+
+    batch, prompt_len, chunk, gen = args.batch_8b, 16384, 2048, 256
+    cfg = dict(LLAMA_8B, num_hidden_layers=args.layers_8b or LLAMA_8B["num_hidden_layers"])
+    layers = cfg["num_hidden_layers"]
+    model = random_model(cfg, args.dtype, seed=8)
+    options = EngineOptions(dtype=args.dtype, block_size=args.block_size,
+                            max_cache_tokens=batch * (prompt_len + gen + 64), max_sequences=batch + 1,
+                            max_batch_size=batch, chunk_size=chunk, max_num_batched_tokens=chunk,
+                            max_model_len=prompt_len + gen + 64, use_cuda_graphs=not args.no_graphs)
+    runner = build_runner(None, options, model=model)
+    cache = runner.cache
+    rng = torch.Generator().manual_seed(88)
+    vocab = cfg["vocab_size"]
+
+    def prefill(rid):
+        ids = torch.randint(0, vocab, (prompt_len,), generator=rng).tolist()
+        cache.add_request(rid)
+        for lo in range(0, prompt_len, chunk):
+            runner.step([StepEntry(rid, ids[lo:lo + chunk], [chunk - 1] if lo + chunk == prompt_len else [])])
+
+    prefill("warm")                             # modules, the rotation table up to 16,384 positions
+    cache.free_request("warm")
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(batch):
+        prefill(("l", i))
+    e1.record()
+    torch.cuda.synchronize()
+    pf_ms = e0.elapsed_time(e1)
+    pf_flops = batch * sum(step_flops(cfg, layers, [(chunk, lo)], 1 if lo + chunk == prompt_len else 0)
+                           for lo in range(0, prompt_len, chunk))
+    rids = [("l", i) for i in range(batch)]
+    warm = 8
+    ids = [torch.randint(0, vocab, (batch,), generator=rng).tolist() for _ in range(gen)]
+    greedy = ([0.0] * batch, [0.0] * batch)
+
+    def one(k):
+        return runner.step([StepEntry(r, [ids[k][i]], [0]) for i, r in enumerate(rids)], sampling=greedy).tokens
+    for k in range(warm):
+        one(k)
+    torch.cuda.synchronize()
+    kv0 = cache.cached_bytes(rids)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for k in range(warm, gen):
+        one(k)
+    e1.record()
+    torch.cuda.synchronize()
+    runner.check_device_errors()
+    dec_ms = e0.elapsed_time(e1) / (gen - warm)
+    kv = (kv0 + cache.cached_bytes(rids)) // 2
+    step_bytes = model.step_weight_bytes() + kv
+    out = {
+        "llama8b_prefill_tok_s": round(batch * prompt_len / (pf_ms / 1e3), 1),
+        "llama8b_prefill_ms_per_portion": round(pf_ms / (batch * prompt_len // chunk), 3),
+        "llama8b_prefill_tensor_frac": round(pf_flops / (pf_ms / 1e3) / (tf_peak * 1e12), 4),
+        "llama8b_decode_tok_s": round(batch / (dec_ms / 1e3), 1),
+        "llama8b_decode_ms_per_step": round(dec_ms, 4),
+        "llama8b_decode_hbm_frac": round(step_bytes / (dec_ms / 1e3) / 1e9 / hbm_peak, 4),
+        "llama8b_batch": batch, "llama8b_context": prompt_len,
+        "llama8b_layers": layers, "llama8b_layers_of_model": LLAMA_8B["num_hidden_layers"],
+    }
+    for r in rids:
+        cache.free_request(r)
+    del runner, model
+    torch.cuda.empty_cache()
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -115,8 +319,13 @@ def main() -> int:
     ap.add_argument("--block-size", type=int, default=16)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--no-graphs", action="store_true")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
-                    help="run one phase only (for profiling); the JSON line then lacks the other figures")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "3b", "8b"],
+                    help="run one phase or workload only (for profiling); the JSON line then lacks the other figures")
+    ap.add_argument("--workloads", default="all", choices=["all", "headline"],
+                    help="headline: leave the 3B and 8B workloads out of points")
+    ap.add_argument("--layers-3b", type=int, default=0, help="fewer layers for the 3B workload (0: all 28)")
+    ap.add_argument("--layers-8b", type=int, default=0, help="fewer layers for the 8B workload (0: all 32)")
+    ap.add_argument("--batch-8b", type=int, default=8)
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -129,6 +338,27 @@ def main() -> int:
     args.steps = max(1, min(args.steps, GEN_LEN - args.warmup - 1))
 
     import torch
+
+    hbm_peak, tf_peak, peak_src = peaks()
+    if args.only in ("3b", "8b"):
+        fn = run_3b_continuous if args.only == "3b" else run_8b_long
+        print(json.dumps({"only": args.only, "points": fn(args, hbm_peak, tf_peak)}))
+        return 0
+    line = run_headline(args, hbm_peak, tf_peak, peak_src)
+    if line is None:
+        return 0
+    if args.workloads == "all":
+        torch.cuda.empty_cache()
+        line["points"].update(run_3b_continuous(args, hbm_peak, tf_peak))
+        line["points"].update(run_8b_long(args, hbm_peak, tf_peak))
+    print(json.dumps(line))
+    return 0
+
+
+def run_headline(args, hbm_peak, tf_peak, peak_src):
+    """The headline: decode at ``--batch`` and the 2,048-token prefill at the Llama 3.2 1B shape, the same
+    through the entry point, batch 1 and 64.  Returns the JSON line as a dict (None: a partial line was printed)."""
+    import torch
     from photon_infer_b200 import EngineOptions
     from photon_infer_b200.engine.engine import ContinuousBatchEngine
     from photon_infer_b200.engine.loading import build_runner
@@ -136,7 +366,6 @@ def main() -> int:
     from photon_infer_b200.kernels import ops
     from photon_infer_b200.weights import write_random_model
 
-    hbm_peak, tf_peak, peak_src = peaks()
     cfg = dict(LLAMA_1B, num_hidden_layers=args.layers)
     torch.manual_seed(0)
     clocks = ClockSampler()
@@ -214,6 +443,18 @@ def main() -> int:
             torch.cuda.profiler.stop()
         pf_ms.append(e0.elapsed_time(e1))
         cache.free_request("p")
+    cut_error = None
+    if pf_ms:
+        # the same 2,048 tokens as one portion and as two of 1,024: the last row's logits must agree
+        # within a rounding of the activations (the kernels differ with the number of rows)
+        cache.add_request("p")
+        whole = runner.step([StepEntry("p", prompt, [PREFILL_TOKENS - 1])]).logits.float().clone()
+        cache.free_request("p")
+        cache.add_request("p")
+        runner.step([StepEntry("p", prompt[:PREFILL_TOKENS // 2], [])])
+        halves = runner.step([StepEntry("p", prompt[PREFILL_TOKENS // 2:], [PREFILL_TOKENS // 2 - 1])]).logits.float()
+        cache.free_request("p")
+        cut_error = float((whole - halves).abs().max() / whole.abs().max())
     prefill_ms = min(pf_ms[1:]) if pf_ms else float("nan")
     H, I, L, d = cfg["hidden_size"], cfg["intermediate_size"], args.layers, cfg["head_dim"]
     nq, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
@@ -221,12 +462,13 @@ def main() -> int:
     attn = 4 * nq * d * (PREFILL_TOKENS * (PREFILL_TOKENS + 1) // 2)          # QK^T and PV over the causal half
     prefill_flops = L * (PREFILL_TOKENS * per_token + attn) + 2 * H * vocab
     prefill = {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
-               "ms": round(prefill_ms, 3), "frac": round(prefill_flops / (prefill_ms / 1e3) / (tf_peak * 1e12), 4)}
+               "ms": round(prefill_ms, 3), "frac": round(prefill_flops / (prefill_ms / 1e3) / (tf_peak * 1e12), 4),
+               "cut_check": None if cut_error is None else round(cut_error, 5)}
 
     if args.only == "prefill":
         clocks.stop()
         print(json.dumps({"only": "prefill", "prefill": prefill}))
-        return 0
+        return None
     # ---- the headline: decode at --batch
     ms_step, kv_bytes, launches, (t0, t1) = decode_region(args.batch, args.steps, args.warmup)
     clock_info = clocks.window(t0, t1)
@@ -238,7 +480,7 @@ def main() -> int:
         print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": round(ms_step, 4),
                           "value": round(value, 1), "roofline_frac": round(achieved / hbm_peak, 4),
                           "gpu_launches": launches}))
-        return 0
+        return None
     points = {}
     if not args.no_points:
         for b in (1, 64):
@@ -285,8 +527,7 @@ def main() -> int:
                      "frac": round(achieved / hbm_peak, 4)},
         "points": points,
     }
-    print(json.dumps(line))
-    return 0
+    return line
 
 
 if __name__ == "__main__":

@@ -32,23 +32,25 @@ class _Request:
 
 class CacheManager:
     def __init__(self, needs: Sequence[Tuple[Optional[PagedCacheSpec], Optional[StateSpec]]],
-                 kv_from: Sequence[Optional[int]], page_size: int, num_pages: int, max_sequences: int,
+                 kv_from: Sequence[Optional[int]], page_size: int, num_pages, max_sequences: int,
                  dtype: torch.dtype = torch.bfloat16, device: Optional[torch.device] = None):
-        """``needs[i]`` / ``kv_from[i]`` describe entry ``i`` of the model's run list."""
+        """``needs[i]`` / ``kv_from[i]`` describe entry ``i`` of the model's run list.  ``num_pages``: one
+        number for every group, or one per group in the order of ``group_specs`` (a group that keeps a
+        window needs far fewer pages than one that keeps everything)."""
         if len(needs) != len(kv_from):
             raise PhotonError(ErrorCode.INVALID_ARGUMENT, "needs and kv_from must have one item per run-list entry")
         self.page_size = page_size
-        self.num_pages = num_pages
         self.max_sequences = max_sequences
         self.dtype = dtype
         self.device = device
-        # group entries by equal page needs, in order of first appearance
-        by_spec: Dict[PagedCacheSpec, List[int]] = {}
-        for i, (pages, _) in enumerate(needs):
-            if pages is not None and kv_from[i] is None:
-                by_spec.setdefault(pages, []).append(i)
-        self.groups: List[CacheGroup] = [CacheGroup(spec, entries, page_size, num_pages, dtype, device)
-                                         for spec, entries in by_spec.items()]
+        specs = self.group_specs(needs, kv_from)
+        counts = [num_pages] * len(specs) if isinstance(num_pages, int) else list(num_pages)
+        if len(counts) != len(specs) or any(int(c) <= 0 for c in counts):
+            raise PhotonError(ErrorCode.INVALID_ARGUMENT,
+                              f"num_pages must be one positive number or one per cache group ({len(specs)} groups)")
+        self.num_pages = max(counts, default=0)
+        self.groups: List[CacheGroup] = [CacheGroup(spec, entries, page_size, int(n), dtype, device)
+                                         for (spec, entries), n in zip(specs, counts)]
         self.entry_location: List[Optional[Tuple[int, int]]] = [None] * len(needs)
         for g, group in enumerate(self.groups):
             for slot, entry in enumerate(group.entries):
@@ -62,6 +64,17 @@ class CacheManager:
                 self.entry_shared[i] = True
         self.states = StateSlotPool(max_sequences, {i: s for i, (_, s) in enumerate(needs) if s is not None}, device)
         self._requests: Dict[object, _Request] = {}
+
+    @staticmethod
+    def group_specs(needs: Sequence[Tuple[Optional[PagedCacheSpec], Optional[StateSpec]]],
+                    kv_from: Sequence[Optional[int]]) -> List[Tuple[PagedCacheSpec, List[int]]]:
+        """The cache groups a run list needs: run-list entries with equal page needs, in order of first
+        appearance.  Entries that read another entry's cache own no pages."""
+        by_spec: Dict[PagedCacheSpec, List[int]] = {}
+        for i, (pages, _) in enumerate(needs):
+            if pages is not None and kv_from[i] is None:
+                by_spec.setdefault(pages, []).append(i)
+        return list(by_spec.items())
 
     # ------------------------------------------------------------------ requests
     def has_request(self, rid) -> bool:

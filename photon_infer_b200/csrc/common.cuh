@@ -64,6 +64,19 @@ __device__ __forceinline__ float block_sum(float v, float* smem32) {
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
 
+// Streaming multiprocessors of the current device (asked once per device; 148 on a B200).
+static inline int photon_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return 148; }
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) { cudaGetLastError(); n = 148; }
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 // ---- programmatic dependent launch: a kernel may be scheduled while its predecessor in the stream drains.
 // Everything it reads that the predecessor wrote must come after pdl_wait(); a kernel launched with
 // launch_pdl must call pdl_wait() on every path, so that completion stays ordered along the stream.

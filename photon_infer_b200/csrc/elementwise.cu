@@ -202,7 +202,8 @@ PHOTON_API int photon_swiglu(const void* gate_up, void* out, int dtype, int T, i
   const bool vec = (I % n == 0) && ((uintptr_t)gate_up % 16 == 0) && ((uintptr_t)out % 16 == 0);
   const size_t work = vec ? total / n : total;
   size_t blocks = (work + threads - 1) / threads;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  const size_t cap = (size_t)photon_sm_count() * 16;
+  if (blocks > cap) blocks = cap;
   if (dtype == PHOTON_BF16) {
     if (vec) swiglu_vec_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, work);
     else swiglu_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, total);

@@ -15,7 +15,8 @@ PHOTON_API const char* photon_static_error_string(int code) {
     case 0: return "ok";
     case PHOTON_STATIC_TOO_LARGE:
       return "the product is larger than the static scratch allows: M <= 64 (32 with SwiGLU), N <= 131072";
-    case PHOTON_ERR_UNSUPPORTED: return "K must be a multiple of 8 and the rows of x and W 16-byte aligned";
+    case PHOTON_ERR_UNSUPPORTED:
+      return "K and the row strides of x and W (ldx, ldw) must be multiples of 8 elements, and x and W 16-byte aligned";
     case PHOTON_ERR_ARGUMENT: return "invalid argument";
     default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown error";
   }
@@ -29,12 +30,13 @@ PHOTON_API int photon_skinny_gemm_static(const void* x, long ldx, const void* W,
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= PHOTON_STATIC_MAX_DEVICES) return PHOTON_ERR_ARGUMENT;
-  unsigned char* base = g_scratch_of_device[dev];
+  // two threads that make the first call together both look the address up and store the same value
+  unsigned char* base = __atomic_load_n(&g_scratch_of_device[dev], __ATOMIC_ACQUIRE);
   if (base == nullptr) {
     // first call on this device: the symbol's address on the current device
     e = cudaGetSymbolAddress((void**)&base, photon_static_scratch);
     if (e != cudaSuccess) return (int)e;
-    g_scratch_of_device[dev] = base;
+    __atomic_store_n(&g_scratch_of_device[dev], base, __ATOMIC_RELEASE);
   }
   int* tickets = reinterpret_cast<int*>(base);
   float* shares = reinterpret_cast<float*>(base + 32768);

@@ -32,7 +32,7 @@ class _InFlight:
     batch: ScheduledBatch
     samplers: List[InferenceRequest]
     tokens: Optional[torch.Tensor]
-    host: Optional[torch.Tensor]
+    host: Optional[torch.Tensor]        # pinned: the sampled ids, then the four words of the error word
     event: Optional["torch.cuda.Event"]
     dropped: set
     report: "StepReport"
@@ -130,13 +130,15 @@ class ContinuousBatchEngine:
         if samplers:
             n = len(samplers)
             slot = self._host_slots[self._launches % 2]
-            if slot is None or slot.numel() < n:
-                slot = self._host_slots[self._launches % 2] = torch.empty(max(n, 256), dtype=torch.int32, pin_memory=True)
-            host = slot[:n]
-            host.copy_(result.tokens, non_blocking=True)
+            if slot is None or slot.numel() < n + 4:
+                slot = self._host_slots[self._launches % 2] = torch.empty(max(n + 4, 260), dtype=torch.int32,
+                                                                         pin_memory=True)
+            host = slot[:n + 4]
+            host[:n].copy_(result.tokens, non_blocking=True)
+            host[n:].copy_(self.runner.error_flag, non_blocking=True)     # read with the ids: no extra wait
             event = torch.cuda.Event()
             event.record()
-            self.d2h_bytes += 4 * n
+            self.d2h_bytes += 4 * (n + 4)
         self._launches += 1
         return _InFlight(batch, samplers, result.tokens, host, event, set(), report)
 
@@ -144,7 +146,10 @@ class ContinuousBatchEngine:
         sampled: Dict[int, int] = {}
         if p.samplers:
             p.event.synchronize()
-            for r, t in zip(p.samplers, p.host.tolist()):
+            values = p.host.tolist()
+            # a bad index or a wait that ran out: the ids of this step come from wrong data
+            self.runner.raise_device_error(values[-4:])
+            for r, t in zip(p.samplers, values[:-4]):
                 if r.request_id not in p.dropped:
                     sampled[r.request_id] = t
         finished = self.scheduler.update_after_step(p.batch, sampled, skip=p.dropped)

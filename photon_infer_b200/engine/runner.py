@@ -9,6 +9,7 @@ here all indices of a step are built once on the host and reach the device in on
 """
 from __future__ import annotations
 
+import collections
 import dataclasses
 from typing import Dict, List, Optional, Sequence
 
@@ -44,6 +45,20 @@ class _DecodeGraph:
     tokens: Optional[torch.Tensor] = None
 
 
+#: Batch sizes that decode graphs are captured for.  A step of single tokens is padded up to the next of
+#: these with copies of its first entry (same token, position, cache slot and block-table row: the copy
+#: computes and stores exactly what the original does, and its logits are dropped), so that a batch that
+#: shrinks by one request replays a graph it already has instead of capturing a new one.
+GRAPH_BATCH_SIZES = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
+
+
+def graph_batch_size(n: int) -> int:
+    for b in GRAPH_BATCH_SIZES:
+        if b >= n:
+            return b
+    return n
+
+
 _DEVICE_ERRORS = {1: "token id {1} at token {0} of the step is outside the vocabulary of {2}",
                   2: "token {0} of the step was given cache slot {1}, outside the pool of {2} slots",
                   3: "token {0} of the step needs key {1}, whose block-table entry is {2}",
@@ -52,12 +67,17 @@ _DEVICE_ERRORS = {1: "token id {1} at token {0} of the step is outside the vocab
 
 class ModelRunner:
     def __init__(self, model: CausalLM, cache: CacheManager, max_model_len: Optional[int] = None,
-                 use_cuda_graphs: bool = False, max_graph_batch: int = 256):
+                 use_cuda_graphs: bool = False, max_graph_batch: int = 256, max_graphs: int = 48):
         self.model = model
-        self.use_cuda_graphs = use_cuda_graphs
+        # A captured step is run once before its capture and replayed with padding rows that repeat a
+        # request; both would advance a mixer's per-request state twice.  Models with such state run
+        # their decode steps as plain launches.
+        self.use_cuda_graphs = use_cuda_graphs and not cache.states.specs
         self.max_graph_batch = max_graph_batch
-        self._graphs: Dict[tuple, "_DecodeGraph"] = {}
+        self.max_graphs = max_graphs        # graphs kept; the one replayed longest ago goes first
+        self._graphs: "collections.OrderedDict[tuple, _DecodeGraph]" = collections.OrderedDict()
         self._graph_pool = None
+        self._pad_indices: Dict[tuple, torch.Tensor] = {}
         self.cache = cache
         self.device = model.device
         self.max_model_len = max_model_len or model.spec.max_position
@@ -135,7 +155,7 @@ class ModelRunner:
         for e in entries:
             cache.commit(e.request_id, len(e.tokens))
         self.steps += 1
-        self.tokens += ctx.num_tokens
+        self.tokens += sum(len(e.tokens) for e in entries)
         return StepResult(logits, rows, tokens)
 
     def _sample(self, logits: torch.Tensor) -> torch.Tensor:
@@ -251,10 +271,19 @@ class ModelRunner:
     def _graph_step(self, entries: Sequence[StepEntry], sampling: Optional[tuple] = None,
                     device_tokens: Optional[torch.Tensor] = None):
         """A step of single tokens replays a captured graph: same kernels, one launch.  A graph is
-        captured per (batch size, block-table width, wanted rows); the width is a power of two of
-        pages, so a graph serves until a request outgrows it.  The logits it returns live in the
-        graph's memory and are overwritten by the next step of the same shape."""
+        captured per (padded batch size, block-table width, wanted rows); the width is a power of two
+        of pages, so a graph serves until a request outgrows it, and the batch is padded to one of
+        ``GRAPH_BATCH_SIZES`` with copies of its first entry.  The logits it returns live in the graph's
+        memory and are overwritten by the next step of the same shape."""
         cache = self.cache
+        real = len(entries)
+        n_want = sum(len(e.want) for e in entries)
+        pad = graph_batch_size(real) - real
+        if pad:
+            entries = list(entries) + [entries[0]] * pad
+            if sampling is not None:
+                extra = pad * len(entries[0].want)
+                sampling = (list(sampling[0]) + [0.0] * extra, list(sampling[1]) + [0.0] * extra)
         rids = [e.request_id for e in entries]
         widths = []
         for w in cache.table_width(rids):
@@ -262,19 +291,35 @@ class ModelRunner:
             while b < w:
                 b *= 2
             widths.append(b)
-        n_want = sum(len(e.want) for e in entries)
-        key = (len(entries), tuple(widths), n_want, sampling is not None)
+        key = (len(entries), tuple(widths), sum(len(e.want) for e in entries), sampling is not None)
         bound = max(w * g.page_size for w, g in zip(widths, cache.groups)) if widths else 1
         graph = self._graphs.get(key)
         if graph is None:
             graph = self._capture(entries, widths, bound, sampling)
             self._graphs[key] = graph
+            while len(self._graphs) > self.max_graphs:
+                self._graphs.popitem(last=False)
+        else:
+            self._graphs.move_to_end(key)
         ctx, _, rows = self._build_context(entries, widths, graph.static_input, bound, sampling)
         if device_tokens is not None:
-            ctx.token_ids.copy_(device_tokens[: ctx.num_tokens])      # a view of the graph's input buffer
+            # into a view of the graph's input buffer; padding rows repeat the first request's id
+            if pad:
+                torch.index_select(device_tokens, 0, self._pad_index(real, pad), out=ctx.token_ids)
+            else:
+                ctx.token_ids.copy_(device_tokens[:real])
         graph.graph.replay()
         self.graph_kernel_launches += graph.kernels
-        return graph.logits, ctx, rows, graph.tokens
+        tokens = graph.tokens[:n_want] if graph.tokens is not None else None
+        return graph.logits[:n_want], ctx, rows[:n_want], tokens
+
+    def _pad_index(self, real: int, pad: int) -> torch.Tensor:
+        key = (real, pad)
+        idx = self._pad_indices.get(key)
+        if idx is None:
+            idx = self._pad_indices[key] = torch.tensor(list(range(real)) + [0] * pad, dtype=torch.int64,
+                                                        device=self.device)
+        return idx
 
     def _capture(self, entries: Sequence[StepEntry], widths: List[int], bound: int,
                  sampling: Optional[tuple] = None) -> "_DecodeGraph":
@@ -302,8 +347,16 @@ class ModelRunner:
     # ------------------------------------------------------------------ errors from the device
     def check_device_errors(self) -> None:
         """Reads the error word the kernels write (a device-to-host copy and a wait)."""
-        flag = self.error_flag.cpu().tolist()
-        if flag[0] != 0:
-            self.error_flag.zero_()
-            msg = _DEVICE_ERRORS.get(flag[0], "device error code {0}").format(flag[1], flag[2], flag[3])
-            raise PhotonError(ErrorCode.INVALID_INDEX, msg)
+        self.raise_device_error(self.error_flag.cpu().tolist())
+
+    def raise_device_error(self, flag: Sequence[int]) -> None:
+        """``flag``: a host copy of the error word.  Non-zero: clears the word and the tickets that a
+        kernel which gave up may have left behind, and raises."""
+        if flag[0] == 0:
+            return
+        from ..kernels import ops
+        self.error_flag.zero_()
+        ops.reset_tickets(self.device)
+        msg = _DEVICE_ERRORS.get(flag[0], "device error code {0}").format(flag[1], flag[2], flag[3])
+        code = ErrorCode.CUDA_ERROR if flag[0] == 4 else ErrorCode.INVALID_INDEX
+        raise PhotonError(code, msg)

@@ -28,6 +28,17 @@ def launch_count() -> int:
     return _launch_count
 
 
+_sm_counts = {}
+
+
+def sm_count(device) -> int:
+    """Streaming multiprocessors of ``device`` (asked once)."""
+    key = (device.type, device.index)
+    if key not in _sm_counts:
+        _sm_counts[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _sm_counts[key]
+
+
 def _dtype_code(t: torch.Tensor) -> int:
     try:
         return _DT[t.dtype]
@@ -222,6 +233,16 @@ def _attention_tickets(device) -> torch.Tensor:
     if key not in _ticket_buffers:
         _ticket_buffers[key] = torch.zeros(1 << 16, dtype=torch.int32, device=device)
     return _ticket_buffers[key]
+
+
+def reset_tickets(device) -> None:
+    """Puts the ticket counters of the split-key attention and of the split-K products back to zero.  The
+    kernels do that themselves after every launch; a launch that gave up (the error word says so) may not."""
+    key = (device.type, device.index)
+    if key in _ticket_buffers:
+        _ticket_buffers[key].zero_()
+    if key in _skinny_buffers:
+        _skinny_buffers[key][1].zero_()
 
 
 def flash_attention_supported(dtype: torch.dtype, head_dim: int) -> bool:

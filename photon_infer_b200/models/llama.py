@@ -49,6 +49,8 @@ def build_llama_spec(cfg: LlamaConfig) -> ModelSpec:
         run=[RunEntry(i) for i in range(cfg.num_hidden_layers)],
         eos_token_ids=tuple(cfg.eos_token_ids),
         bos_token_id=cfg.bos_token_id,
+        # older exports store the rotation frequencies as a buffer of every layer; they follow from rope_theta
+        ignored_tensors=("*.rotary_emb.inv_freq",),
     )
 
 

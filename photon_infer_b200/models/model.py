@@ -148,6 +148,8 @@ class CausalLM:
         T = ctx.num_tokens
         residual = torch.empty((T, self.spec.hidden_size), dtype=torch.float32, device=self.device)
         ops.embedding(ctx.token_ids, self.embedding, residual, ctx.error_flag)
+        if self.spec.embedding_scale is not None:
+            residual.mul_(self.spec.embedding_scale)
         delta = None
         for entry, cache in zip(self.spec.run, caches):
             residual, delta = self.blocks[entry.layer].forward(residual, delta, ctx, cache)
@@ -156,4 +158,7 @@ class CausalLM:
             # the blocks still ran: their cache writes are the step's effect
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         y = self.final_norm.add_forward_rows(delta, residual, logit_rows, self.dtype)
-        return ops.linear(y, self.head, out_dtype=torch.float32)
+        logits = ops.linear(y, self.head, out_dtype=torch.float32)
+        if self.spec.logit_scale is not None:
+            logits.mul_(self.spec.logit_scale)
+        return logits

@@ -50,6 +50,12 @@ class ModelSpec:
     run: List[RunEntry]
     eos_token_ids: tuple = ()
     bos_token_id: Optional[int] = None
+    # name patterns of tensors that weight files of this architecture may carry and the model does not use
+    ignored_tensors: tuple = ()
+    # optional factors: the embedded rows are multiplied by ``embedding_scale`` before the first block, the
+    # logits by ``logit_scale`` after the head (architectures that scale either; None: untouched)
+    embedding_scale: Optional[float] = None
+    logit_scale: Optional[float] = None
 
     def validate(self) -> None:
         from ..errors import ErrorCode, PhotonError

@@ -158,7 +158,7 @@ class PagedAttention(Mixer):
                 keys = ctx.max_context_len if self.window is None else min(self.window, ctx.max_context_len)
                 if self._max_groups is None:
                     self._max_groups = ops.flash_attention_max_groups(self.head_dim)
-                splits, groups = choose_key_shares(sum(few) * self.n_kv, keys, self._max_groups)
+                splits, groups = choose_key_shares(sum(few) * self.n_kv, keys, self._max_groups, sms=ops.sm_count(q.device))
                 if splits > 1:
                     scratch = torch.empty(T * self.n_q * splits * (self.head_dim + 2), dtype=torch.float32, device=q.device)
             if rows_mode and ops.USE_ATTENTION_TC and \
@@ -178,7 +178,7 @@ class PagedAttention(Mixer):
                             self.n_q, self.n_kv, self.head_dim, self.window, self.scale, ctx.error_flag)
 
 
-def choose_key_shares(pairs: int, max_keys: int, max_groups: int, tile: int = 64, sms: int = 148):
+def choose_key_shares(pairs: int, max_keys: int, max_groups: int, tile: int = 64, sms: int = 148):  # sms: the caller passes the device's count
     """How the keys of a decoded token are shared out: (blocks per (request, key/value head), groups of
     four warps per block).  Measured on B200 (148 SMs) at 32/8 heads of 64:
 

@@ -8,7 +8,9 @@ float32, which is exact for bfloat16 and float16 files.
 """
 from __future__ import annotations
 
-from typing import Dict
+import fnmatch
+import sys
+from typing import Dict, Sequence
 
 import torch
 
@@ -30,9 +32,17 @@ def target_dtype(spec: TensorSpec, stored: torch.dtype, run_dtype: torch.dtype) 
 
 
 def check_names_and_shapes(declared: Dict[str, TensorSpec], found: Dict[str, tuple], dtypes: Dict[str, torch.dtype],
-                           where: str) -> None:
+                           where: str, ignorable: Sequence[str] = ()) -> None:
+    """``ignorable``: name patterns (``fnmatch``) of tensors that some exports of the architecture carry
+    and the model has no use for (buffers that are recomputed from the configuration); they are named
+    in one line on stderr instead of counting as unexpected."""
     missing = sorted(n for n in declared if n not in found)
     unexpected = sorted(n for n in found if n not in declared)
+    ignored = [n for n in unexpected if any(fnmatch.fnmatchcase(n, pat) for pat in ignorable)]
+    if ignored:
+        unexpected = [n for n in unexpected if n not in ignored]
+        print(f"[photon] warning: {len(ignored)} tensors in {where} are not used and were skipped: "
+              + ", ".join(ignored[:4]) + (", ..." if len(ignored) > 4 else ""), file=sys.stderr, flush=True)
     wrong = []
     for n, spec in declared.items():
         if n in found:
@@ -54,12 +64,12 @@ def check_names_and_shapes(declared: Dict[str, TensorSpec], found: Dict[str, tup
 
 
 def load_tensors(folder: str, declared: Dict[str, TensorSpec], run_dtype: torch.dtype,
-                 device) -> Dict[str, torch.Tensor]:
+                 device, ignorable: Sequence[str] = ()) -> Dict[str, torch.Tensor]:
     """``declared`` maps full tensor names to their specs; returns device tensors by name."""
     entries, files = open_model_files(folder)
     try:
         check_names_and_shapes(declared, {n: e.shape for n, e in entries.items()},
-                               {n: e.dtype for n, e in entries.items()}, folder)
+                               {n: e.dtype for n, e in entries.items()}, folder, ignorable)
         out: Dict[str, torch.Tensor] = {}
         for name, spec in declared.items():
             e = entries[name]

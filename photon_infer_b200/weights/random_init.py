@@ -72,3 +72,33 @@ def write_random_model(folder: str, config, seed: int = 0, init_std: float = 0.0
     write_safetensors(os.path.join(folder, "model.safetensors"), tensors,
                       metadata={"format": "pt", "seed": seed, "init_std": init_std, "norm_std": norm_std})
     return {n: tuple(t.shape) for n, t in tensors.items()}
+
+
+def random_tensors_on_device(declared: Dict[str, TensorSpec], run_dtype: torch.dtype, device, seed: int = 0,
+                             init_std: float = 0.02, norm_std: float = 0.0) -> Dict[str, torch.Tensor]:
+    """The tensors a model declares, drawn on the device itself: for measurements at sizes whose weight file
+    would take longer to write and read than the run (a Llama 3.1 8B shape is 16 GB).  Same distributions as
+    ``write_random_model`` and the same storage rule as the loader, but the device's generator: the values
+    differ from those of a folder written with the same seed."""
+    dev = torch.device(device)
+    out: Dict[str, torch.Tensor] = {}
+    for i, (name, spec) in enumerate(declared.items()):
+        g = torch.Generator(device=dev)
+        digest = hashlib.sha256(f"{seed}:{name}".encode()).digest()
+        g.manual_seed(int.from_bytes(digest[:8], "little") & 0x7FFFFFFFFFFFFFFF)
+        if spec.role == "int":
+            out[name] = torch.zeros(spec.shape, dtype=torch.int32, device=dev)
+            continue
+        dtype = torch.float32 if (run_dtype == torch.float32 or spec.role == "vector") else run_dtype
+        if spec.init == "zeros":
+            t = torch.zeros(spec.shape, dtype=dtype, device=dev)
+        elif spec.init == "norm":
+            t = torch.ones(spec.shape, dtype=dtype, device=dev)
+            if norm_std > 0:
+                t += norm_std * torch.randn(spec.shape, generator=g, dtype=dtype, device=dev)
+        elif spec.init == "normal":
+            t = torch.empty(spec.shape, dtype=dtype, device=dev).normal_(0.0, init_std, generator=g)
+        else:
+            raise PhotonError(ErrorCode.INVALID_ARGUMENT, f"tensor {name}: unknown init {spec.init!r}")
+        out[name] = t
+    return out

@@ -87,7 +87,7 @@ int main(int argc, char** argv) {
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="a checkout of lumia431/photon_infer (its include/ folder is compiled against)")
     ap.add_argument("--out", default=os.path.join(os.path.dirname(__file__), "reference_tiny.npz"))
     args = ap.parse_args()
     c = CFG

@@ -125,16 +125,26 @@ def test_mixed(session):
 
 
 def test_cuts_agree(session):
-    """The logits at a position do not depend on how the request was cut, beyond rounding."""
-    if "whole" not in session.collected:
-        pytest.skip("needs the other tests of the module")
-    tol = 1e-6 if session.dtype == "float32" else 1.5e-2
+    """The logits at a position do not depend on how the request was cut.  In float32 every sum of the
+    path has an order that depends only on the token's position (products: one chain of K multiply-adds;
+    norms: the block size follows the width; attention: key tiles aligned at multiples of 32 from key 0),
+    so the four ways of cutting must agree to the bit.  In bfloat16 the kernels differ with the number of
+    rows (weight streaming, tcgen05, the library) and the bound is a rounding of the activations."""
+    for label, fn in (("whole", test_whole), ("tail", test_tail_one_by_one), ("portions", test_portions),
+                      ("mixed", test_mixed)):
+        if label not in session.collected:
+            fn(session)                                     # run alone: make what is compared
     for label in ("tail", "portions", "mixed"):
         for rid, (_, ref) in session.collected["whole"].items():
-            if rid in session.collected.get(label, {}):
-                other = session.collected[label][rid][1]
+            other = session.collected[label][rid][1]
+            if session.dtype == "float32":
+                same = np.array_equal(other, ref)
+                where = None if same else int(np.argwhere((other != ref).any(axis=1))[0, 0])
+                assert same, f"{label} against whole, request {rid}: first position that differs {where}, " \
+                    f"largest difference {float(np.abs(other - ref).max()):.3g}"
+            else:
                 err = rel_err(torch.from_numpy(other), torch.from_numpy(ref))
-                assert err <= tol, f"{label} against whole, request {rid}: {err:.3g}"
+                assert err <= 1.5e-2, f"{label} against whole, request {rid}: {err:.3g}"
 
 
 def test_nothing_wanted_writes_no_file(session):

@@ -78,6 +78,25 @@ def test_one_error_lists_missing_unexpected_and_wrong(tmp_path):
     assert "model.embed_tokens.weight" in msg and "floating point" in msg
 
 
+def test_buffers_some_exports_carry_are_skipped_with_a_warning(tmp_path, capsys):
+    """Older Llama exports store every layer's rotation frequencies; the architecture names the pattern and the
+    loader skips them with one line on stderr.  Any other extra tensor is still an error."""
+    from photon_infer_b200.config.registry import get_architecture
+    folder = make_model_folder(str(tmp_path), "tiny_a")
+    arch = get_architecture("LlamaForCausalLM")
+    spec = arch.build_spec(arch.config_class.from_dict(TINY["tiny_a"]["config"]))
+    tensors = _read_all(folder)
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(8)
+    tensors["model.layers.1.self_attn.rotary_emb.inv_freq"] = torch.ones(8)
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
+    got = load_tensors(folder, _declared("tiny_a"), torch.bfloat16, "cpu", spec.ignored_tensors)
+    assert "rotary_emb.inv_freq" not in " ".join(got)
+    assert "2 tensors" in capsys.readouterr().err
+    with pytest.raises(PhotonError) as e:
+        load_tensors(folder, _declared("tiny_a"), torch.bfloat16, "cpu")
+    assert "unexpected (2)" in str(e.value)
+
+
 def test_untied_model_needs_its_head(tmp_path):
     folder = make_model_folder(str(tmp_path), "tiny_b")
     tensors = _read_all(folder)

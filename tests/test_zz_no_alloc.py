@@ -41,8 +41,10 @@ def test_static_scratch_entry_point_matches_the_regular_one_twice_in_a_row():
     torch.manual_seed(31)
     # (M, N, K, epilogue): K = 8192 with few rows splits K over blocks (scratch and tickets in use);
     # the second call has other sizes and finds what the first one left in the array
-    cases = [(8, 2048, 8192, "bf16"), (3, 520, 4104, "f32"), (8, 2048, 8192, "bf16"), (5, 1024, 512, "swiglu")]
-    for M, N, K, epi in cases:
+    # the largest N the array has tickets for, and the largest M, are among the cases
+    cases = [(8, 2048, 8192, "bf16"), (3, 520, 4104, "f32"), (8, 2048, 8192, "bf16"), (5, 1024, 512, "swiglu"),
+             (2, 131072, 64, "f32"), (64, 528, 1024, "bf16")]
+    for n_call, (M, N, K, epi) in enumerate(cases):
         x = torch.randn(M, K, device=DEV).bfloat16()
         w = (torch.randn(N, K, device=DEV) / K ** 0.5).bfloat16()
         cols = N // 2 if epi == "swiglu" else N
@@ -50,9 +52,14 @@ def test_static_scratch_entry_point_matches_the_regular_one_twice_in_a_row():
         want = torch.empty(M, cols, dtype=dtype, device=DEV)
         ops.skinny_gemm(x, w, want, epi)
         got = torch.full((M, cols), float("nan"), dtype=dtype, device=DEV)
+        torch.cuda.synchronize()
+        free_before, held_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
         code = _call(lib, x, w, got, {"bf16": 0, "f32": 1, "swiglu": 2}[epi])
         assert code == 0, lib.photon_static_error_string(code).decode()
         torch.cuda.synchronize()
+        if n_call > 0:
+            # the set-up of the first call is behind us: a call takes no device memory, from the driver or from torch
+            assert torch.cuda.mem_get_info()[0] == free_before and torch.cuda.memory_allocated() == held_before
         ref = x.double() @ w.double().t()
         if epi == "swiglu":
             ref = ref[:, :cols] / (1 + torch.exp(-ref[:, :cols])) * ref[:, cols:]
