@@ -48,9 +48,47 @@ LLAMA_8B = dict(LLAMA_1B, hidden_size=4096, intermediate_size=14336, num_hidden_
 PROMPT_LEN, GEN_LEN, CONTEXT, PREFILL_TOKENS = 512, 256, 4096, 2048
 PUBLISHED_BATCH8_TOK_S = 720.0       # the reference's README: batch 8, A100, INT8 weights
 
-REFERENCE_UNAVAILABLE = ("lumia431/photon_infer is a CMake/C++ project without a Python package (pip finds no "
-                         "setup.py or pyproject.toml) and needs glog, Eigen and gtest, which are not installed; "
-                         "no network")
+REFERENCE_BINARY = os.path.join(ROOT, "baseline", "_ref", "bin", "photon_ref_bench")
+
+
+def run_reference(args) -> int:
+    """The reference arm: lumia431/photon_infer, unmodified, built by ``baseline/build_reference.sh`` with its
+    own CMake project, driven through its own API by ``baseline/reference_bench.cpp``.  Nothing of this
+    package runs on that path.  Prints the harness's JSON line with the clocks seen meanwhile, or an
+    ``unavailable`` line when the binary is not there or does not run."""
+    def unavailable(why: str) -> int:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    if args.gpus != 1:
+        return unavailable("lumia431/photon_infer runs on one GPU only")
+    if not os.path.isfile(REFERENCE_BINARY):
+        return unavailable("pip cannot install lumia431/photon_infer (a CMake/C++ project without setup.py or "
+                           "pyproject.toml); its CMake build, baseline/build_reference.sh <checkout>, has not been run here")
+    clocks = ClockSampler()
+    clocks.start()
+    t0 = time.monotonic()
+    try:
+        proc = subprocess.run([REFERENCE_BINARY, "--batch", str(args.batch), "--steps", str(max(1, args.steps)),
+                               "--warmup", str(max(3, args.warmup)), "--prompt", str(PROMPT_LEN),
+                               "--generated", str(GEN_LEN)],
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=900)
+    except (OSError, subprocess.TimeoutExpired) as e:
+        clocks.stop()
+        return unavailable(f"the reference's binary did not run to its end: {type(e).__name__}")
+    t1 = time.monotonic()
+    clocks.stop()
+    sys.stderr.write(proc.stderr[-2000:])
+    lines = [ln for ln in proc.stdout.splitlines() if ln.startswith("{")]
+    if proc.returncode != 0 or not lines:
+        return unavailable(f"the reference's binary ended with code {proc.returncode}: {proc.stderr.strip()[-200:]}")
+    line = json.loads(lines[-1])
+    if "unavailable" not in line:
+        # the timed decode steps are the last part of the run
+        line["clocks"] = clocks.window(max(t0, t1 - 2.0), t1)
+        line["vs_baseline"] = round(line["value"] / PUBLISHED_BATCH8_TOK_S, 2) if args.batch == 8 else None
+        line["gpu_launches"] = 0            # none of this package's kernels: the reference's own and cuBLAS
+    print(json.dumps(line))
+    return 0
 
 
 def peaks():
@@ -329,8 +367,7 @@ def main() -> int:
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
-        return 0
+        return run_reference(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
