@@ -315,6 +315,83 @@ def flash_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
         _launch_count += 1
 
 
+def attention_decode_supported(dtype: torch.dtype, head_dim: int, group: int, page_size: int, num_seqs: int) -> bool:
+    """The persistent TMA kernel for decoded tokens: bfloat16, head size 64 or 128, up to 16 heads per
+    key/value head, pages of 8, 16, 32 or a multiple of 64 tokens, up to 512 requests in the step."""
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and 1 <= group <= 16 and num_seqs <= 512
+            and page_size % 8 == 0 and page_size >= 8 and (64 % page_size == 0 or page_size % 64 == 0))
+
+
+def attention_decode_slots(head_dim: int) -> int:
+    """Blocks of the persistent decode-attention kernel that the current device holds at once."""
+    lib = load_module("attention_decode", {"HEAD_DIM": head_dim})
+    return int(lib.photon_attention_decode_slots())
+
+
+def attention_decode_plan(num_seqs: int, n_kv: int, max_keys: int, head_dim: int, page_size: int):
+    """(tiles of 64 keys per work item, chunks to reserve scratch for, upper bound of the work items) for a step of
+    ``num_seqs`` requests of at most ``max_keys`` visible keys; None when a request has more keys than the kernel
+    takes (about 490,000).  A request is cut into as few chunks as fill the
+    GPU once: measured on B200, every cut costs a partial result written, a ticket and a merge, so 64 requests of
+    640 keys run best whole (26 us against 45 us in chunks of four tiles), while 8 requests of 16,500 keys and 8
+    key/value heads need five chunks each to give every block work (95 us against 154 us in chunks of four)."""
+    slots = attention_decode_slots(head_dim)
+    tiles = -(-max(max_keys, 1) // 64) + 1              # a window may start inside a tile
+    most = 64                                           # tiles an item may have
+    fewest = -(-tiles // most)
+    per_seq = max(1, slots // max(1, num_seqs * n_kv), fewest)
+    per_seq = min(per_seq, 120, max(fewest, tiles // 4))        # no item shorter than four tiles, 120 chunks at most
+    chunk = max(1, -(-tiles // per_seq))
+    per_seq = -(-tiles // chunk)
+    if per_seq > 120:
+        return None                                     # more keys than 120 chunks of 64 tiles hold
+    return chunk, num_seqs * per_seq, num_seqs * per_seq * n_kv
+
+
+def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                     block_table: torch.Tensor, cu_tokens: torch.Tensor, context_lens: torch.Tensor, num_seqs: int,
+                     n_q: int, n_kv: int, head_dim: int, window: Optional[int], scale: float, chunk_tiles: int,
+                     scratch: torch.Tensor, scratch_chunks: int, max_items: int, err: Optional[torch.Tensor]) -> None:
+    """Attention of the requests that bring at most 16 rows (tokens x heads per group) in this step, by the
+    persistent TMA kernel (``attention_decode.cu``); the rows of the other requests are left untouched.
+    ``context_lens [S]``: tokens of each request after this step (a request's tokens of the step are its last).
+    ``scratch``: float32, at least ``scratch_chunks * n_kv * 16 * (head_dim + 2)``; ``scratch_chunks`` at least the
+    chunks of ``chunk_tiles`` tiles that all requests have together (``attention_decode_plan``)."""
+    _cuda(q, out, k_cache, v_cache, block_table, cu_tokens, context_lens, scratch, err)
+    T = q.shape[0]
+    if n_kv <= 0 or n_q % n_kv or not attention_decode_supported(q.dtype, head_dim, n_q // n_kv, k_cache.shape[2], num_seqs):
+        raise PhotonError(ErrorCode.UNSUPPORTED_SIZE,
+                          f"attention_decode: head_dim {head_dim}, {n_q}/{n_kv} heads, pages of {k_cache.shape[2]} in {q.dtype} is not supported")
+    if q.shape[1] != n_q * head_dim or q.stride(1) != 1 or out.shape != (T, n_q * head_dim) or not out.is_contiguous():
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "attention_decode: q and out must be [T, n_q * head_dim]")
+    if out.dtype != q.dtype or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "attention_decode: q, out and the caches must be bfloat16")
+    if not k_cache.is_contiguous() or not v_cache.is_contiguous() or k_cache.shape != v_cache.shape:
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, "attention_decode: the caches must be contiguous [pages, n_kv, page, d]")
+    for name, t in (("block_table", block_table), ("cu_tokens", cu_tokens), ("context_lens", context_lens)):
+        _int32(t, name)
+    if cu_tokens.numel() < num_seqs + 1 or block_table.shape[0] < num_seqs or context_lens.numel() < num_seqs:
+        raise PhotonError(ErrorCode.SHAPE_MISMATCH, "attention_decode: cu_tokens, context_lens and block_table must cover every request")
+    need = scratch_chunks * n_kv * 16 * (head_dim + 2)
+    if scratch.dtype != torch.float32 or scratch.numel() < need or not scratch.is_contiguous():
+        raise PhotonError(ErrorCode.INVALID_ARGUMENT, f"attention_decode: scratch must hold {need} float32 values")
+    tickets = _attention_tickets(q.device)
+    if tickets.numel() < num_seqs * n_kv + 2:      # the tickets, then the kernel's two work counters
+        raise PhotonError(ErrorCode.UNSUPPORTED_SIZE, "attention_decode: too many requests for the ticket buffer")
+    part_ml = scratch[scratch_chunks * n_kv * 16 * head_dim:]
+    f = _fn("attention_decode", "photon_attention_decode",
+            [c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+             c_long, c_void_p, c_void_p],
+            defines={"HEAD_DIM": head_dim})
+    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+             block_table.shape[1], _ptr(cu_tokens), _ptr(context_lens), _ptr(scratch), _ptr(part_ml), int(scratch_chunks),
+             _ptr(tickets), int(num_seqs), T, n_q, n_kv, head_dim, k_cache.shape[2], k_cache.shape[0],
+             int(window) if window else 0, float(scale), int(chunk_tiles), max(1, -(-int(scratch_chunks) // max(num_seqs, 1))),
+             int(max_items), _ptr(err), _stream()),
+           "attention_decode")
+
+
 # PHOTON_ATTENTION_TC=0 keeps prompt portions on the mma.sync kernel (for comparisons)
 USE_ATTENTION_TC = os.environ.get("PHOTON_ATTENTION_TC", "1") != "0"
 

@@ -498,6 +498,95 @@ def test_flash_attention_far_key_and_window_edge():
         assert hit == visible, (far, window, count)
 
 
+def _decode_attention_case(n_q, n_kv, d, ps, window, lens, counts, chunk, seed=41, spike=None):
+    """Requests of `lens` tokens whose last `counts[i]` tokens are this step's; the persistent TMA kernel with work
+    items of `chunk` tiles, against float64.  Cache slots the step must not see hold NaN."""
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(seed)
+    dtype = torch.bfloat16
+    pages = sum((L + ps - 1) // ps for L in lens) + 3
+    kc = torch.full((pages, n_kv, ps, d), float("nan"), dtype=dtype)
+    vc = torch.full_like(kc, float("nan"))
+    perm = torch.randperm(pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    width = max((L + ps - 1) // ps for L in lens) + 1
+    table = torch.full((len(lens), width), -1, dtype=torch.int32)
+    qs, want, cu = [], [], [0]
+    for i, (L, count) in enumerate(zip(lens, counts)):
+        q = torch.randn(L, n_q, d)
+        k = torch.randn(L, n_kv, d)
+        v = torch.randn(L, n_kv, d)
+        if spike is not None and i == 0:
+            k *= 0.1; q *= 0.1
+            k[spike] = 0; k[spike, :, 0] = 40.0; q[:, :, 0] = 40.0
+        q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
+        for lp in range((L + ps - 1) // ps):
+            table[i, lp] = perm.pop()
+        for t in range(L):
+            kc[table[i, t // ps], :, t % ps] = k[t]
+            vc[table[i, t // ps], :, t % ps] = v[t]
+        o = causal_attention(q.double(), k.double(), v.double(), window=window)
+        qs.append(q[L - count:]); want.append(o[L - count:])
+        cu.append(cu[-1] + count)
+    T = cu[-1]
+    q = torch.cat(qs).reshape(T, n_q * d)
+    out = torch.full((T, n_q * d), float("nan"), dtype=dtype, device=DEV)
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    keys = max(lens) if window is None else min(window + max(counts), max(lens))
+    chunks = len(lens) * (-(-(keys // 64 + 2) // chunk))
+    scratch = torch.full((chunks * n_kv * 16 * (d + 2),), float("nan"), device=DEV)
+    for _ in range(2):                                      # twice: the tickets and counters must be back at zero
+        out.fill_(float("nan"))
+        ops.attention_decode(q.to(DEV), out, kc.to(DEV), vc.to(DEV), table.to(DEV),
+                             torch.tensor(cu, dtype=torch.int32, device=DEV),
+                             torch.tensor(lens, dtype=torch.int32, device=DEV), len(lens), n_q, n_kv, d, window,
+                             1.0 / math.sqrt(d), chunk, scratch, chunks, chunks * n_kv, err)
+        assert err.cpu().tolist()[0] == 0
+        assert not torch.isnan(out.float()).any()
+        _close(out, torch.cat(want).reshape(T, n_q * d), dtype)
+    return out.float().cpu(), torch.cat(want).reshape(T, n_q * d)
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,ps,window", [
+    (32, 8, 64, 16, None), (24, 8, 128, 16, None), (3, 1, 64, 8, None), (8, 1, 128, 32, None), (6, 2, 64, 64, None),
+    (16, 1, 64, 16, None), (6, 2, 64, 16, 70), (4, 2, 128, 128, 200)])
+def test_decode_attention_tma(n_q, n_kv, d, ps, window):
+    """Single tokens of requests of very different lengths (one key, a page's edge, a tile's edge, thousands of
+    keys), and short portions of up to 16 rows, with items of 1, 4 and 64 tiles: one chunk, many chunks merged."""
+    lens = [640, 1, 65, 333, 2100, 64, 63, 129, 1024]
+    G = n_q // n_kv
+    for chunk in (1, 4, 64):
+        _decode_attention_case(n_q, n_kv, d, ps, window, lens, [1] * len(lens), chunk)
+    if 16 // G >= 2:
+        counts = [min(L, 16 // G) if i % 2 else 1 for i, L in enumerate(lens)]
+        _decode_attention_case(n_q, n_kv, d, ps, window, lens, counts, 4)
+
+
+def test_decode_attention_tma_far_key_and_more_requests_than_blocks():
+    """A key far back must carry the result (chunks merged with their true weights), and a step with more work
+    items than the GPU has blocks must hand every one of them out."""
+    for far in (0, 63, 64, 1000, 2099):
+        got, want = _decode_attention_case(4, 1, 64, 16, None, [2100, 300], [1, 1], 4, spike=far)
+        assert float((got[0] - want[0].float()).abs().max()) < 2e-2
+    lens = [70 + 13 * i for i in range(200)]
+    _decode_attention_case(8, 4, 64, 16, None, lens, [1] * len(lens), 1)
+
+
+def test_decode_attention_tma_refuses_what_it_cannot_take():
+    from photon_infer_b200.errors import PhotonError
+    from photon_infer_b200.kernels import ops
+    assert not ops.attention_decode_supported(torch.bfloat16, 48, 3, 16, 4)
+    assert not ops.attention_decode_supported(torch.float32, 64, 4, 16, 4)
+    assert not ops.attention_decode_supported(torch.bfloat16, 64, 32, 16, 4)
+    assert not ops.attention_decode_supported(torch.bfloat16, 64, 4, 24, 4)
+    assert not ops.attention_decode_supported(torch.bfloat16, 64, 4, 16, 600)
+    q = torch.zeros(1, 48, dtype=torch.bfloat16, device=DEV)
+    kc = torch.zeros(4, 1, 16, 48, dtype=torch.bfloat16, device=DEV)
+    z = torch.zeros(2, dtype=torch.int32, device=DEV)
+    with pytest.raises(PhotonError):
+        ops.attention_decode(q, q.clone(), kc, kc.clone(), torch.zeros(1, 8, dtype=torch.int32, device=DEV), z, z, 1, 1, 1,
+                             48, None, 1.0, 4, torch.zeros(4096, device=DEV), 1, 1, None)
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1, 8, 8), (100, 300, 72), (257, 513, 520), (2048, 3072, 2048),
                                    (333, 389, 120), (4096, 256, 8192)])
 def test_gemm_tcgen05(M, N, K):
