@@ -44,7 +44,7 @@ def test_static_scratch_entry_point_matches_the_regular_one_twice_in_a_row():
     # the largest N the array has tickets for, and the largest M, are among the cases
     cases = [(8, 2048, 8192, "bf16"), (3, 520, 4104, "f32"), (8, 2048, 8192, "bf16"), (5, 1024, 512, "swiglu"),
              (2, 131072, 64, "f32"), (64, 528, 1024, "bf16")]
-    for n_call, (M, N, K, epi) in enumerate(cases):
+    for M, N, K, epi in cases:
         x = torch.randn(M, K, device=DEV).bfloat16()
         w = (torch.randn(N, K, device=DEV) / K ** 0.5).bfloat16()
         cols = N // 2 if epi == "swiglu" else N
@@ -52,14 +52,19 @@ def test_static_scratch_entry_point_matches_the_regular_one_twice_in_a_row():
         want = torch.empty(M, cols, dtype=dtype, device=DEV)
         ops.skinny_gemm(x, w, want, epi)
         got = torch.full((M, cols), float("nan"), dtype=dtype, device=DEV)
+        code = _call(lib, x, w, got, {"bf16": 0, "f32": 1, "swiglu": 2}[epi])
+        assert code == 0, lib.photon_static_error_string(code).decode()
         torch.cuda.synchronize()
+        # The same call once more.  The set-up of the first call on this device is behind us and the driver has
+        # loaded this kernel variant's code (it does that at a variant's first launch): now a call must leave
+        # the device's free memory and torch's allocator exactly as they were.
+        first = got.clone()
         free_before, held_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
         code = _call(lib, x, w, got, {"bf16": 0, "f32": 1, "swiglu": 2}[epi])
         assert code == 0, lib.photon_static_error_string(code).decode()
         torch.cuda.synchronize()
-        if n_call > 0:
-            # the set-up of the first call is behind us: a call takes no device memory, from the driver or from torch
-            assert torch.cuda.mem_get_info()[0] == free_before and torch.cuda.memory_allocated() == held_before
+        assert torch.cuda.mem_get_info()[0] == free_before and torch.cuda.memory_allocated() == held_before
+        assert torch.equal(got, first)
         ref = x.double() @ w.double().t()
         if epi == "swiglu":
             ref = ref[:, :cols] / (1 + torch.exp(-ref[:, :cols])) * ref[:, cols:]
