@@ -25,10 +25,12 @@ from typing import Dict, Iterable, Optional, Tuple
 from ..errors import ErrorCode, PhotonError
 
 CSRC_DIR = os.path.dirname(os.path.abspath(__file__))
+INCLUDE_DIR = os.path.join(os.path.dirname(CSRC_DIR), "include")          # photon/kernels.h
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-shared", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden"]
-ALL_MODULES = ("elementwise", "rope_kv", "attention", "gemm_f32", "gemm_skinny", "gemm_skinny_fused", "gemm_skinny_static", "gemm_tc", "gemm_tc2", "sampling")
+ALL_MODULES = ("elementwise", "rope_kv", "attention", "gemm_f32", "gemm_skinny", "gemm_skinny_fused", "gemm_skinny_static",
+               "gemm_tc", "gemm_tc2", "sampling")
 
 _loaded: Dict[Tuple[str, Tuple[Tuple[str, str], ...]], ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -85,6 +87,8 @@ def _source_hash(module: str, defines: Tuple[Tuple[str, str], ...], extra_flags:
                 (name.endswith(".cu") and name != f"{module}.cu" and module.startswith(name[:-3])):
             with open(os.path.join(CSRC_DIR, name), "rb") as f:
                 h.update(f.read())
+    with open(os.path.join(INCLUDE_DIR, "photon", "kernels.h"), "rb") as f:
+        h.update(f.read())
     h.update(repr((ARCH_FLAGS, BASE_FLAGS, defines, extra_flags)).encode())
     return h.hexdigest()[:12]
 
@@ -107,7 +111,7 @@ def compile_module(module: str, defines: Optional[Dict[str, object]] = None,
         return out
     nvcc = find_nvcc()
     tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
-    cmd = [nvcc, *ARCH_FLAGS, *BASE_FLAGS, *extra_flags, "-I", CSRC_DIR]
+    cmd = [nvcc, *ARCH_FLAGS, *BASE_FLAGS, *extra_flags, "-I", CSRC_DIR, "-I", INCLUDE_DIR]
     for k, v in sorted((defines or {}).items()):
         cmd.append(f"-D{k}={v}")
     if verbose:
@@ -175,7 +179,9 @@ def ensure_built(modules: Iterable[object]) -> None:
 
 
 # specialisations that the build check compiles besides the plain modules (the Llama 3.2 1B shape)
-DEFAULT_SPECIALISATIONS = (("attention_flash", {"HEAD_DIM": 64}), ("attention_tc", {"HEAD_DIM": 64}))
+DEFAULT_SPECIALISATIONS = (("attention_flash", {"HEAD_DIM": 64}), ("attention_tc", {"HEAD_DIM": 64}),
+                           ("attention_decode", {"HEAD_DIM": 64}), ("attention_flash", {"HEAD_DIM": 128}),
+                           ("attention_tc", {"HEAD_DIM": 128}), ("attention_decode", {"HEAD_DIM": 128}))
 
 
 def build_all(verbose: bool = False) -> None:

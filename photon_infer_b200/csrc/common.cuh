@@ -6,21 +6,12 @@
 #include <stdint.h>
 #include <stdlib.h>
 
+// The exported entry points, the dtype codes shared with kernels/ops.py, the launcher's return codes and the
+// codes that kernels write into the error word: declared once, for C callers too.  A definition below that
+// does not match its declaration there is a compile error.
+#include <photon/kernels.h>
+
 #define PHOTON_API extern "C" __attribute__((visibility("default")))
-
-// dtype codes shared with kernels/ops.py
-#define PHOTON_F32 0
-#define PHOTON_BF16 1
-
-// launcher return codes below zero are argument errors found on the host
-#define PHOTON_ERR_UNSUPPORTED (-2)
-#define PHOTON_ERR_ARGUMENT (-3)
-
-// codes that kernels write into the error word (int32[4]: code, detail0, detail1, detail2)
-#define PHOTON_DEV_BAD_TOKEN 1
-#define PHOTON_DEV_BAD_SLOT 2
-#define PHOTON_DEV_BAD_PAGE 3
-#define PHOTON_DEV_WAIT_TIMEOUT 4
 
 typedef __nv_bfloat16 bf16;
 
