@@ -45,14 +45,20 @@ static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "head size of the tcgen05 atten
 #define AT_ROWS 128
 #define AT_KT 64                                   // keys per tile
 #ifndef AT_STAGES
-#define AT_STAGES 3
+#define AT_STAGES (HEAD_DIM == 64 ? 3 : 2)          // two blocks per SM either way (97 KB each at heads of 128)
+#endif
+#ifndef AT_BLOCKS_PER_SM
+#define AT_BLOCKS_PER_SM 2
 #endif
 #define AT_THREADS 192                             // warps 0-3: softmax, warp 4: TMA, warp 5: MMA + TMEM
 #define AT_DH (HEAD_DIM / 64)                      // 64-wide halves of the head dimension
 #define AT_Q_BYTES (AT_ROWS * HEAD_DIM * 2)
 #define AT_KV_BYTES (AT_KT * HEAD_DIM * 2)         // one K tile or one V tile
 #define AT_HALF_BYTES (AT_KT * 128)                // one 64-wide half of a K or V tile
-#define AT_P_BYTES (AT_ROWS * AT_KT * 2)
+#ifndef AT_P_TMEM
+#define AT_P_TMEM 1                                // 1: P stays in tensor memory (it takes the place of the scores it came from)
+#endif
+#define AT_P_BYTES (AT_P_TMEM ? 0 : AT_ROWS * AT_KT * 2)
 #define AT_SMEM_BYTES (AT_Q_BYTES + AT_STAGES * 2 * AT_KV_BYTES + 2 * AT_P_BYTES + 1024 + 256)
 #define AT_TMEM_COLS 256                           // scores 2 x 64 columns, O from column 128
 #define AT_O_COL 128
@@ -68,6 +74,11 @@ struct AttnTcParams {
   int* err;
 };
 
+// D += A B with A in tensor memory (128 lanes x 8 columns of packed bfloat16 pairs per 16 of K), B in shared memory.
+__device__ __forceinline__ void at_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+               ::"r"(d_tmem), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ float at_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -94,7 +105,7 @@ __device__ __forceinline__ uint32_t at_pack(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__global__ void __launch_bounds__(AT_THREADS, HEAD_DIM == 64 ? 2 : 1)
+__global__ void __launch_bounds__(AT_THREADS, AT_BLOCKS_PER_SM)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const AttnTcParams P) {
   // ---- which rows: uniform for the block, before anything is set up
@@ -224,9 +235,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const uint32_t p_addr = tc_smem(p_s + (i & 1) * AT_P_BYTES);
         const uint32_t v_addr = tc_smem(kv_s + s * 2 * AT_KV_BYTES + AT_KV_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < AT_KT / 16; ++kk)    // 16 keys: 32 bytes along a row of P, two groups of 8 rows of V
-          tc_mma(tmem_base + AT_O_COL, tc_desc(p_addr + kk * 32), tc_desc_mn(v_addr + kk * 2048, AT_HALF_BYTES, 1024),
-                 idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < AT_KT / 16; ++kk) {  // 16 keys: two groups of 8 rows of V
+          if (AT_P_TMEM)                           // P: 8 columns of packed pairs per 16 keys, where the tile's scores were
+            at_mma_ts(tmem_base + AT_O_COL, tmem_base + (i & 1) * AT_KT + kk * 8, tc_desc_mn(v_addr + kk * 2048, AT_HALF_BYTES, 1024),
+                      idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+          else                                     // P: 32 bytes along a row of the swizzled tile in shared memory
+            tc_mma(tmem_base + AT_O_COL, tc_desc(p_addr + kk * 32), tc_desc_mn(v_addr + kk * 2048, AT_HALF_BYTES, 1024),
+                   idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+        }
         tc_commit(&kv_empty[s]);
         tc_commit(&pv_done[i & 1]);
       }
@@ -315,15 +331,22 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           *reinterpret_cast<uint4*>(vst + half * AT_HALF_BYTES + (nvalid + (rem >> 3)) * 128 + ((rem & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
       }
-      // the P buffer is free once the products of tile i - 2 have read it
-      if (i >= 2 && !wait_all(&pv_done[b], ((i - 2) >> 1) & 1)) { ok = false; break; }
-      unsigned char* prow = p_s + b * AT_P_BYTES + r * 128;
+      if (AT_P_TMEM) {
+        // P over the scores it came from (this thread has them in registers; the next scores for this buffer are
+        // issued after the product that reads P)
+        tc_st32(lane_addr + b * AT_KT, pk);
+        tc_st_wait();
+      } else {
+        // the P buffer is free once the products of tile i - 2 have read it
+        if (i >= 2 && !wait_all(&pv_done[b], ((i - 2) >> 1) & 1)) { ok = false; break; }
+        unsigned char* prow = p_s + b * AT_P_BYTES + r * 128;
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        uint4 v4 = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
-        *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = v4;
+        for (int ch = 0; ch < 8; ++ch) {
+          uint4 v4 = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+          *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = v4;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> the tensor core's reads
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes -> the tensor core's reads
       tc_fence_before();
       __syncwarp();
       if (lane == 0) tc_mbar_arrive(&p_full[b]);
