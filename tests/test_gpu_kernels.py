@@ -54,7 +54,7 @@ def test_embedding_reports_bad_token():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,H", [(1, 16), (7, 200), (3, 2048), (2, 5000), (2, 14000)])
+@pytest.mark.parametrize("T,H", [(1, 16), (7, 200), (3, 2048), (2, 5000), (2, 14000), (300, 2048), (70, 200), (65, 4100)])
 @pytest.mark.parametrize("w_dtype", [torch.float32, torch.bfloat16])
 def test_add_rmsnorm(dtype, T, H, w_dtype):
     from photon_infer_b200.kernels import ops
@@ -80,6 +80,13 @@ def test_add_rmsnorm(dtype, T, H, w_dtype):
     out3 = torch.empty(T, H, dtype=dtype, device=DEV)
     ops.add_rmsnorm(None, r2, w.to(DEV), eps, out3)
     _close(out3, rms_norm(res.double(), w.double(), eps), dtype)
+    if T >= 64:
+        # many listed rows (the kernel with a warp per row, in bfloat16): every row twice, backwards
+        many = torch.arange(T - 1, -1, -1, dtype=torch.int32, device=DEV).repeat(2)
+        out4 = torch.empty(2 * T, H, dtype=dtype, device=DEV)
+        ops.add_rmsnorm(delta.to(DEV), r2, w.to(DEV), eps, out4, rows=many)
+        assert torch.equal(r2.cpu(), res)
+        _close(out4, want[many.cpu().long()], dtype)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
