@@ -113,52 +113,6 @@ __global__ void add_rmsnorm_kernel(const TD* delta, float* residual,          //
   }
 }
 
-// Many rows (prompt portions), bfloat16 output: a warp per row, two passes over the row (the second finds it in
-// L1), no shared memory and no block-wide barrier.  One block per row costs 2,048 blocks of a few hundred bytes
-// of work each at 2,048 rows (11.5 us at a width of 2,048 against 6 us here).
-template <typename TD, typename TO>
-__global__ void __launch_bounds__(256)
-add_rmsnorm_rows_kernel(const TD* delta, float* residual, const void* __restrict__ w, int w_bf16, TO* out,
-                        const int* rows, int n, int H, float eps) {
-  pdl_wait();
-  const int lane = threadIdx.x & 31;
-  const int idx = blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (idx >= n) return;
-  const int r = rows ? rows[idx] : idx;
-  float* res = residual + (size_t)r * H;
-  const TD* d = delta ? delta + (size_t)r * H : nullptr;
-  float ss = 0.f;
-  for (int i = lane * 4; i < H; i += 128) {
-    float v[4], dv[4];
-    Quad<float>::load(res + i, v);
-    if (d) {
-      Quad<TD>::load(d + i, dv);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) v[e] += dv[e];
-    }
-#pragma unroll
-    for (int e = 0; e < 4; ++e) ss += v[e] * v[e];
-  }
-  ss = warp_sum(ss);
-  pdl_launch_dependents();
-  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
-  TO* o = out + (size_t)idx * H;
-  for (int i = lane * 4; i < H; i += 128) {
-    float v[4], dv[4], wv[4], y[4];
-    Quad<float>::load(res + i, v);
-    if (d) {
-      Quad<TD>::load(d + i, dv);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) v[e] += dv[e];
-      if (!rows) Quad<float>::store(res + i, v);
-    }
-    if (w_bf16) Quad<bf16>::load((const bf16*)w + i, wv); else Quad<float>::load((const float*)w + i, wv);
-#pragma unroll
-    for (int e = 0; e < 4; ++e) y[e] = wv[e] * (v[e] * inv);
-    Quad<TO>::store(o + i, y);
-  }
-}
-
 template <typename TD, typename TO>
 static int add_rmsnorm_launch(const void* delta, float* residual, const void* w, int w_bf16, void* out,
                               const int* rows, int n, int H, float eps, cudaStream_t stream) {
@@ -173,11 +127,6 @@ static int add_rmsnorm_launch(const void* delta, float* residual, const void* w,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  // bfloat16 activations and many rows: a warp per row.  (The float32 path keeps one kernel for every number of
-  // rows, so that a row's sum has the same order however the request was cut into steps.)
-  if (vec && sizeof(TO) == 2 && n >= 64)
-    return launch_pdl(add_rmsnorm_rows_kernel<TD, TO>, dim3((n + 7) / 8), dim3(256), 0, stream, (const TD*)delta, residual,
-                      w, w_bf16, (TO*)out, rows, n, H, eps);
   int threads = 128;
   while (threads < 1024 && threads * 4 < H) threads <<= 1;   // depends on H only
   if (vec)

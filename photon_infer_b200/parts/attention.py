@@ -159,8 +159,10 @@ class PagedAttention(Mixer):
             keys = ctx.max_context_len if self.window is None else min(self.window + ctx.max_query_len, ctx.max_context_len)
             # decoded tokens with long contexts: the persistent TMA kernel
             plan = None
-            if keys_mode and keys >= DECODE_TMA_MIN_KEYS.get(self.head_dim, 1 << 30) and ops.attention_decode_supported(
-                    q.dtype, self.head_dim, gsize, cache.k.shape[2], ctx.num_seqs):
+            pairs = sum(few) * self.n_kv
+            if keys_mode and (keys >= DECODE_TMA_MIN_KEYS.get(self.head_dim, 1 << 30)
+                              or pairs * keys >= DECODE_TMA_MIN_WORK.get(self.head_dim, 1 << 60)) \
+                    and ops.attention_decode_supported(q.dtype, self.head_dim, gsize, cache.k.shape[2], ctx.num_seqs):
                 plan = ops.attention_decode_plan(sum(few), self.n_kv, keys, self.head_dim, cache.k.shape[2])
             decode_tma = plan is not None
             if keys_mode and not decode_tma:
@@ -204,6 +206,12 @@ class PagedAttention(Mixer):
 #: every batch size tried (8 x 16,500 keys: 95 us against 156 us; 56 x 1,300: 63 against 112); heads of 64 move
 #: half the bytes per tile and only gain with very long contexts (4 x 32,000 keys: 53 us against 68 us).
 DECODE_TMA_MIN_KEYS = {128: 1000, 64: 8192}
+#: ... or from this many (request, key/value head) pairs x keys on: with many requests the persistent kernel wins
+#: earlier, because the split-key kernel has one block per pair and each block keeps a single tile in flight.
+#: Measured with cold caches at 24/8 heads of 128: 64 requests x 256 keys 25 us against 30 us, x 768 keys 45 against
+#: 73; 32 x 512: 23 against 24; 16 x 768: 23 against 18 (still the split-key kernel).  Heads of 64, 64 requests:
+#: x 1,024 keys 36 against 34, x 2,048 keys 59 against 62.
+DECODE_TMA_MIN_WORK = {128: 128 * 1024, 64: 1024 * 1024}
 
 
 def choose_key_shares(pairs: int, max_keys: int, max_groups: int, tile: int = 64, sms: int = 148):  # sms: the caller passes the device's count

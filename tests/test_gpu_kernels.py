@@ -81,7 +81,7 @@ def test_add_rmsnorm(dtype, T, H, w_dtype):
     ops.add_rmsnorm(None, r2, w.to(DEV), eps, out3)
     _close(out3, rms_norm(res.double(), w.double(), eps), dtype)
     if T >= 64:
-        # many listed rows (the kernel with a warp per row, in bfloat16): every row twice, backwards
+        # many listed rows: every row twice, backwards
         many = torch.arange(T - 1, -1, -1, dtype=torch.int32, device=DEV).repeat(2)
         out4 = torch.empty(2 * T, H, dtype=dtype, device=DEV)
         ops.add_rmsnorm(delta.to(DEV), r2, w.to(DEV), eps, out4, rows=many)
