@@ -355,6 +355,8 @@ def main() -> int:
     ap.add_argument("--impl", default="photon_b200", choices=["photon_b200", "reference"])
     ap.add_argument("--dtype", default="bfloat16")
     ap.add_argument("--block-size", type=int, default=16)
+    ap.add_argument("--shape", default="1b", choices=["1b", "3b", "8b"],
+                    help="layer sizes of the single steps that --only decode / --only prefill time (for profiles)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "3b", "8b"],
@@ -403,7 +405,10 @@ def run_headline(args, hbm_peak, tf_peak, peak_src):
     from photon_infer_b200.kernels import ops
     from photon_infer_b200.weights import write_random_model
 
-    cfg = dict(LLAMA_1B, num_hidden_layers=args.layers)
+    shapes = {"1b": LLAMA_1B, "3b": LLAMA_3B, "8b": LLAMA_8B}
+    if args.shape != "1b" and args.only not in ("decode", "prefill"):
+        raise SystemExit("--shape 3b/8b goes with --only decode or --only prefill (a profile of single steps)")
+    cfg = dict(shapes[args.shape], num_hidden_layers=min(args.layers, shapes[args.shape]["num_hidden_layers"]))
     torch.manual_seed(0)
     clocks = ClockSampler()
     clocks.start()

@@ -87,6 +87,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (lane == 0) {
       int it = 0;                                   // k blocks issued so far
       bool ok = true;
+#ifdef TC_TEST_NO_LOADS
+      ok = false;                                   // test build: nothing is ever loaded, so the waits below run out
+#endif
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile / tiles_n) * TC_BM, n0 = (tile % tiles_n) * TILE_COLS;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {

@@ -7,8 +7,9 @@
 
 The shapes are those of the Llama 3.2 1B layer unless ``--hidden/--intermediate/--heads/--kv-heads/
 --head-dim`` say otherwise.  Decode kernels are timed inside a CUDA graph of ten launches over ten
-different weight (or cache) buffers, so that neither host gaps nor a warm L2 flatter them; the
-library product (cuBLAS through ``torch.mm``) is timed the same way beside ours.
+different weight (or cache) buffers, with a buffer larger than L2 written before every timed replay, so
+that neither host gaps nor a warm L2 flatter them; the library product (cuBLAS through ``torch.mm``) is
+timed the same way beside ours.
 """
 from __future__ import annotations
 
@@ -46,7 +47,23 @@ def _graph(fn, copies: int, reps: int = 10) -> float:
         for i in range(copies):
             fn(i)
     g.replay()
-    return _events(g.replay, reps=reps, warm=2) / copies
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    times = []
+    for _ in range(reps):
+        _flush.zero_()                                   # 256 MB: what the last replay left in L2 is gone
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3 / copies)
+    times.sort()
+    return times[len(times) // 2]
+
+
+_flush = None
 
 
 def _shapes(a):
@@ -138,7 +155,7 @@ def attention_decode(a) -> None:
             pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
             lens = torch.full((B,), ctx, dtype=torch.int32, device=dev)
             err = torch.zeros(4, dtype=torch.int32, device=dev)
-            splits, groups = choose_key_shares(B * n_kv, ctx, max_groups)
+            splits, groups = choose_key_shares(B * n_kv, ctx, max_groups, sms=ops.sm_count(dev))
             scratch = torch.empty(B * n_q * splits * (d + 2), device=dev)
 
             def one(i):
@@ -147,8 +164,22 @@ def attention_decode(a) -> None:
                                     splits, scratch, False, True, err, lens, groups)
             t = _graph(one, 10)
             mb = B * ctx * n_kv * d * 2 * 2 / 1e6
-            print(f"batch {B:3d} context {ctx:6d}  blocks per pair {splits:2d}, groups {groups}: {t:7.2f} us "
-                  f"for {mb:7.1f} MB of keys and values ({mb / t:5.2f} TB/s)", flush=True)
+            line = (f"batch {B:3d} context {ctx:6d}  {mb:7.1f} MB of keys and values: split-key kernel ({splits} blocks per pair, "
+                    f"{groups} groups) {t:7.2f} us ({mb / t:5.2f} TB/s)")
+            plan = None
+            if ops.attention_decode_supported(q.dtype, d, n_q // n_kv, a.page_size, B):
+                plan = ops.attention_decode_plan(B, n_kv, ctx, d, a.page_size)
+            if plan is not None:
+                chunk, chunks, items = plan
+                scratch2 = torch.empty(chunks * n_kv * 16 * (d + 2), device=dev)
+
+                def two(i):
+                    kc, vc, table = caches[i % len(caches)]
+                    ops.attention_decode(q, out, kc, vc, table, cu, lens, B, n_q, n_kv, d, None, 1.0 / math.sqrt(d), chunk,
+                                         scratch2, chunks, items, err)
+                t2 = _graph(two, 10)
+                line += f"   persistent TMA kernel (chunks of {chunk} tiles) {t2:7.2f} us ({mb / t2:5.2f} TB/s)"
+            print(line, flush=True)
 
 
 def main(argv=None) -> int:

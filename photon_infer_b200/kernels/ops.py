@@ -331,20 +331,31 @@ def attention_decode_slots(head_dim: int) -> int:
 def attention_decode_plan(num_seqs: int, n_kv: int, max_keys: int, head_dim: int, page_size: int):
     """(tiles of 64 keys per work item, chunks to reserve scratch for, upper bound of the work items) for a step of
     ``num_seqs`` requests of at most ``max_keys`` visible keys; None when a request has more keys than the kernel
-    takes (about 490,000).  A request is cut into as few chunks as fill the
-    GPU once: measured on B200, every cut costs a partial result written, a ticket and a merge, so 64 requests of
-    640 keys run best whole (26 us against 45 us in chunks of four tiles), while 8 requests of 16,500 keys and 8
-    key/value heads need five chunks each to give every block work (95 us against 154 us in chunks of four)."""
+    takes (about 490,000).
+
+    A request's keys are cut into ``p`` chunks; a (chunk, key/value head) is a work item that one of the resident
+    blocks draws.  ``p`` minimises ``rounds * (tiles per item + 5) + 0.3 * p`` with ``rounds = ceil(items / blocks)``:
+    an item costs about five tile times beside its tiles (Q, the first round trip, the merge of its four warps), a
+    chunk a partial result written and merged, and what decides most is how many items the busiest block gets.
+    Measured on B200: 64 requests of 640 keys run best whole (26 us against 45 us in chunks of four tiles); 8
+    requests x 8 heads of 16,500 keys: five chunks each are 320 items for 296 blocks, two rounds of 52 tiles (95
+    us), chunks of four tiles 154 us."""
     slots = attention_decode_slots(head_dim)
     tiles = -(-max(max_keys, 1) // 64) + 1              # a window may start inside a tile
     most = 64                                           # tiles an item may have
-    fewest = -(-tiles // most)
-    per_seq = max(1, slots // max(1, num_seqs * n_kv), fewest)
-    per_seq = min(per_seq, 120, max(fewest, tiles // 4))        # no item shorter than four tiles, 120 chunks at most
-    chunk = max(1, -(-tiles // per_seq))
-    per_seq = -(-tiles // chunk)
-    if per_seq > 120:
+    pairs = max(1, num_seqs * n_kv)
+    best = None
+    for p in range(-(-tiles // most), min(120, tiles) + 1):
+        chunk = -(-tiles // p)
+        if -(-tiles // chunk) != p:
+            continue                                    # the same chunk length as a smaller p
+        rounds = -(-(pairs * p) // slots)
+        cost = rounds * (chunk + 5) + (0.3 * p if p > 1 else 0.0)
+        if best is None or cost < best[0]:
+            best = (cost, chunk, p)
+    if best is None:
         return None                                     # more keys than 120 chunks of 64 tiles hold
+    _, chunk, per_seq = best
     return chunk, num_seqs * per_seq, num_seqs * per_seq * n_kv
 
 

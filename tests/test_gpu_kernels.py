@@ -620,6 +620,38 @@ def test_gemm_tcgen05(M, N, K):
     assert err.cpu().tolist()[0] == 0
 
 
+def test_gemm_tcgen05_wait_that_runs_out_is_reported():
+    """A build of gemm_tc.cu whose producer loads nothing (``TC_TEST_NO_LOADS``) and whose waits give up after a
+    few thousand polls: the consumer's bounded wait on a barrier that nothing completes runs out, the kernel
+    records PHOTON_DEV_WAIT_TIMEOUT with the block's index, frees its tensor memory and returns; the stock
+    build runs right afterwards in the same context."""
+    import ctypes
+    from ctypes import c_int, c_long, c_void_p
+    from photon_infer_b200.csrc.build import load_module
+    from photon_infer_b200.kernels import ops
+    torch.manual_seed(16)
+    M, N, K = 256, 512, 128
+    x = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).bfloat16()
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    lib = load_module("gemm_tc", {"TC_TEST_NO_LOADS": 1, "TC_WAIT_LIMIT": 4096})
+    f = lib.photon_gemm_tc
+    f.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+    f.restype = c_int
+    status = f(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, N, K, 0,
+               err.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert status == 0
+    torch.cuda.synchronize()                                   # the kernel came back by itself
+    word = err.cpu().tolist()
+    assert word[0] == 4 and 0 <= word[1] < 4                   # PHOTON_DEV_WAIT_TIMEOUT, one of the four blocks
+    assert float(out.float().abs().max()) == 0.0               # nothing was computed, nothing was written
+    err.zero_()
+    ops.gemm_tc(x, w, out, "bf16", err)                        # tensor memory and barriers are in order
+    _close(out, x.double() @ w.double().t(), torch.bfloat16)
+    assert err.cpu().tolist()[0] == 0
+
+
 @pytest.mark.parametrize("M,I,K", [(128, 128, 64), (70, 200, 96), (2048, 8192, 2048), (300, 136, 72)])
 def test_gemm_tcgen05_swiglu(M, I, K):
     from photon_infer_b200.kernels import ops
