@@ -47,7 +47,7 @@ static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "head size of the TMA decode at
 #define AD_KD (HEAD_DIM / 16)
 #define AD_ND (HEAD_DIM / 8)
 #define AD_MAX_SEQS 512
-#define AD_MAX_CHUNKS 120                           // chunks of one request: 16 rows x 120 weights fit the merge buffer; a lane holds four
+#define AD_MAX_CHUNKS (HEAD_DIM < 120 ? HEAD_DIM : 120)   // chunks of one request: 16 rows x (chunks + 1) weights fit the merge buffer of 16 x (HEAD_DIM + 2) floats; a lane holds four
 #define AD_Q_BYTES (16 * HEAD_DIM * 2)              // the 16 query rows
 #define AD_MERGE_BYTES (16 * (HEAD_DIM + 2) * 4)    // one warp's partial result
 #define AD_SMEM_BYTES (AD_STAGES * AD_STAGE_BYTES + AD_Q_BYTES + AD_MERGE_BYTES + 1024)
@@ -82,6 +82,7 @@ struct DecodeParams {
                                            // blocks that are done; all zero between launches
   int S, n_kv, group, page_size, num_pages, total_rows, box_rows, window, chunk_tiles;
   int q_rows;                              // rows of the Q box: GROUP * floor(16 / GROUP)
+  int T;                                   // tokens of the step (rows of q and out)
   float scale_log2;
   int* err;
 };
@@ -234,7 +235,12 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     int mine = 0;
     for (int seq = s_lo; seq < s_hi; ++seq) {
       int tok0, ntok, ctx, tb, te;
-      const int n = key_range(seq, tok0, ntok, ctx, tb, te) ? (te - tb + CH - 1) / CH : 0;
+      int n = key_range(seq, tok0, ntok, ctx, tb, te) ? (te - tb + CH - 1) / CH : 0;
+      if (n > AD_MAX_CHUNKS || (n > 0 && (tok0 < 0 || tok0 + ntok > P.T))) {
+        // more chunks than the merge takes, or tokens outside the step: the request is skipped and reported
+        report_error(P.err, PHOTON_DEV_BAD_SLOT, seq, n, tok0);
+        n = 0;
+      }
       chunk_prefix[seq + 1] = n;                                 // counts first, sums below
       mine += n;
     }
@@ -680,6 +686,7 @@ PHOTON_API int photon_attention_decode(const void* q, long q_stride, void* out, 
   P.block_table = block_table; P.max_pages = max_pages; P.cu_tokens = cu_tokens; P.context_lens = context_lens;
   P.part_acc = part_acc; P.part_ml = part_ml; P.scratch_chunks = scratch_chunks; P.tickets = tickets;
   P.q_rows = G * (16 / G);
+  P.T = T;
   P.S = S; P.n_kv = n_kv; P.group = G; P.page_size = page_size; P.num_pages = num_pages;
   P.total_rows = (int)total_rows; P.box_rows = box_rows; P.window = window; P.chunk_tiles = chunk_tiles;
   P.scale_log2 = scale * 1.4426950408889634f; P.err = err;

@@ -345,7 +345,7 @@ def attention_decode_plan(num_seqs: int, n_kv: int, max_keys: int, head_dim: int
     most = 64                                           # tiles an item may have
     pairs = max(1, num_seqs * n_kv)
     best = None
-    for p in range(-(-tiles // most), min(120, tiles) + 1):
+    for p in range(-(-tiles // most), min(120, head_dim, tiles) + 1):     # the kernel merges up to min(120, head_dim) chunks
         chunk = -(-tiles // p)
         if -(-tiles // chunk) != p:
             continue                                    # the same chunk length as a smaller p
@@ -357,6 +357,22 @@ def attention_decode_plan(num_seqs: int, n_kv: int, max_keys: int, head_dim: int
         return None                                     # more keys than 120 chunks of 64 tiles hold
     _, chunk, per_seq = best
     return chunk, num_seqs * per_seq, num_seqs * per_seq * n_kv
+
+
+_decode_scratch = {}
+
+
+def attention_decode_scratch(device, floats: int) -> torch.Tensor:
+    """The partial results of ``attention_decode``: one float32 buffer per device of at least ``floats`` elements.
+    It grows by doubling and the buffers it outgrew are kept, because a captured CUDA graph holds the address it
+    was captured with; a tensor that died with the step would leave the graph writing into memory that has a
+    new owner."""
+    key = (device.type, device.index)
+    buffers = _decode_scratch.setdefault(key, [])
+    if not buffers or buffers[-1].numel() < floats:
+        size = max(int(floats), 2 * buffers[-1].numel() if buffers else 0, 1 << 20)
+        buffers.append(torch.empty(size, dtype=torch.float32, device=device))
+    return buffers[-1]
 
 
 def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,

@@ -180,13 +180,9 @@ class PagedAttention(Mixer):
                 rows_mode = False
             if decode_tma:
                 chunk, chunks, items = plan
-                need = chunks * self.n_kv * 16 * (self.head_dim + 2)
-                # one scratch buffer per step, shared by the layers (they run one after the other)
-                if not isinstance(ctx.scratch, dict):
-                    ctx.scratch = {}
-                scratch = ctx.scratch.get("attention_decode")
-                if scratch is None or scratch.numel() < need:
-                    scratch = ctx.scratch["attention_decode"] = torch.empty(need, dtype=torch.float32, device=q.device)
+                # one scratch buffer per device, shared by the layers and steps (they run one after the other) and never
+                # freed: a captured decode step keeps its address
+                scratch = ops.attention_decode_scratch(q.device, chunks * self.n_kv * 16 * (self.head_dim + 2))
                 ops.attention_decode(q, out, cache.k, cache.v, group.block_table, ctx.cu_tokens, ctx.context_lens,
                                      ctx.num_seqs, self.n_q, self.n_kv, self.head_dim, self.window, self.scale, chunk,
                                      scratch, chunks, items, ctx.error_flag)

@@ -250,3 +250,47 @@ def test_pipelined_decode_equals_step_by_step(folders):
     assert a[1][1] == "length" and len(a[1][0]) == 5
     assert a[3][0] == m.greedy(prompts[3], 33)
     assert eng_a._inflight is None
+
+
+def test_captured_decode_steps_keep_their_scratch(tmp_path, monkeypatch):
+    """Decode steps replayed as CUDA graphs with the persistent attention kernel (forced here at short contexts,
+    chunks of one tile, so that partial results go through its scratch buffer): the buffer a captured step writes
+    to must stay owned after the step that captured it is gone.  Tensors allocated after the capture are the
+    victims if it does not: they must stay zero, and the replayed steps must agree with the plain implementation."""
+    from helpers import TINY, TOL, make_model_folder, plain_logits, random_ids, rel_err
+    from photon_infer_b200 import EngineOptions
+    from photon_infer_b200.engine.loading import build_runner
+    from photon_infer_b200.engine.runner import StepEntry
+    from photon_infer_b200.kernels import ops
+    from photon_infer_b200.parts import attention
+    folder = make_model_folder(str(tmp_path / "m"), "tiny_d")
+    vocab = TINY["tiny_d"]["config"]["vocab_size"]
+    monkeypatch.setattr(attention, "DECODE_TMA_MIN_KEYS", {64: 1})
+    monkeypatch.setattr(ops, "attention_decode_plan", lambda n, n_kv, keys, d, page: (1, n * (keys // 64 + 2), n * (keys // 64 + 2) * n_kv))
+    seen = []
+    real = ops.attention_decode
+
+    def spy(*a, **kw):
+        seen.append(a[14])                                   # the scratch tensor of this launch
+        return real(*a, **kw)
+    monkeypatch.setattr(ops, "attention_decode", spy)
+    runner = build_runner(folder, EngineOptions(dtype="bfloat16", block_size=32, max_cache_tokens=4096, max_sequences=8,
+                                                use_cuda_graphs=True))
+    seqs = [random_ids(150 + 37 * i, vocab, seed=70 + i) for i in range(3)]
+    for i, ids in enumerate(seqs):
+        runner.cache.add_request(i)
+        runner.step([StepEntry(i, ids[:-4], [])])
+    victims = []
+    for k in range(4):                                       # four decode steps: the first captures, the others replay
+        got = runner.step([StepEntry(i, [seqs[i][len(seqs[i]) - 4 + k]], [0]) for i in range(3)]).logits.float().cpu()
+        for i, ids in enumerate(seqs):
+            want = plain_logits(folder, ids[: len(ids) - 3 + k])[-1:]
+            assert rel_err(got[i: i + 1], want) <= TOL["bfloat16"], (k, i)
+        for v in victims:
+            assert float(v.abs().max()) == 0.0               # nobody wrote into memory that has a new owner
+        # what the allocator hands out now is what a freed scratch buffer would have left behind
+        victims += [torch.zeros(n, dtype=torch.float32, device="cuda:0") for n in (1 << 12, 1 << 14, 1 << 16, 1 << 18, 1 << 20)]
+    runner.check_device_errors()
+    assert seen and runner.graph_kernel_launches > 0
+    owned = {t.data_ptr() for t in ops._decode_scratch[("cuda", 0)]}
+    assert all(t.data_ptr() in owned for t in seen)
