@@ -331,7 +331,7 @@ def attention_decode_slots(head_dim: int) -> int:
 def attention_decode_plan(num_seqs: int, n_kv: int, max_keys: int, head_dim: int, page_size: int):
     """(tiles of 64 keys per work item, chunks to reserve scratch for, upper bound of the work items) for a step of
     ``num_seqs`` requests of at most ``max_keys`` visible keys; None when a request has more keys than the kernel
-    takes (about 490,000).
+    takes (min(120, head size) chunks of 64 tiles of 64 keys: about 490,000 at heads of 128, 260,000 at heads of 64).
 
     A request's keys are cut into ``p`` chunks; a (chunk, key/value head) is a work item that one of the resident
     blocks draws.  ``p`` minimises ``rounds * (tiles per item + 5) + 0.3 * p`` with ``rounds = ceil(items / blocks)``:
