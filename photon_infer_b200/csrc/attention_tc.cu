@@ -4,7 +4,7 @@
 // A block owns up to 128 query rows of one request that share a key/value head
 // (row = token_in_step * GROUP + head_in_group, as in attention_flash.cu; floor(128 / GROUP)
 // whole tokens) and walks the
-// request's keys in tiles of 64:
+// request's keys in tiles of 64 (AT_KT):
 //   * warp 4 brings the rows of Q (one 3-D TMA box) and then the key and value tiles of the
 //     paged cache (one TMA box per page part, the block table followed by the lanes of the
 //     warp) into a ring of shared-memory stages, 128-byte swizzle;
@@ -12,8 +12,8 @@
 //     buffers in tensor memory, and O += P V (M 128, N = head size; V is read as it lies in
 //     the cache, keys along the rows, through an MN-major descriptor);
 //   * warps 0-3 own one row per thread: they read the scores with tcgen05.ld, keep the
-//     running maximum and sum in 32-bit, write P = exp2(..) as bfloat16 into shared memory
-//     (the swizzled layout the next product reads), and rescale O in tensor memory only when
+//     running maximum and sum in 32-bit, write P = exp2(..) as bfloat16 back over the scores in
+//     tensor memory (the second product takes its A operand from there), and rescale O in tensor memory only when
 //     a row's maximum has grown by more than 2^8 since the last rescale (the sum and O stay
 //     relative to the maximum in use, so the result is the same up to rounding).
 // The scores of tile i + 1 are computed while the softmax of tile i runs.
@@ -43,9 +43,17 @@
 static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "head size of the tcgen05 attention");
 
 #define AT_ROWS 128
-#define AT_KT 64                                   // keys per tile
+// Keys per tile.  -DAT_KT=128 (heads of 64 only: two stages of such tiles leave room for two blocks per SM) halves the
+// hand-overs per key, but tensor memory then holds ONE score buffer beside O, so the scores of the next tile wait
+// for P V of this one: measured 47.5 us against 38.6 us at 2,048 tokens, 522 against 427 us at 8,192.
+#ifndef AT_KT
+#define AT_KT 64
+#endif
+static_assert(AT_KT == 64 || HEAD_DIM == 64, "tiles of 128 keys only at heads of 64");
+static_assert(AT_KT == 64 || AT_KT == 128, "keys per tile");
+#define AT_NBUF (AT_KT == 128 ? 1 : 2)             // score buffers in tensor memory (128 columns in all)
 #ifndef AT_STAGES
-#define AT_STAGES (HEAD_DIM == 64 ? 3 : 2)          // two blocks per SM either way (97 KB each at heads of 128)
+#define AT_STAGES (HEAD_DIM * AT_KT == 64 * 64 ? 3 : 2)   // two blocks per SM either way (81 KB, or 97 KB at heads of 128)
 #endif
 #ifndef AT_BLOCKS_PER_SM
 #define AT_BLOCKS_PER_SM 2
@@ -59,8 +67,9 @@ static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "head size of the tcgen05 atten
 #define AT_P_TMEM 1                                // 1: P stays in tensor memory (it takes the place of the scores it came from)
 #endif
 #define AT_P_BYTES (AT_P_TMEM ? 0 : AT_ROWS * AT_KT * 2)
+static_assert(AT_P_TMEM || AT_KT == 64, "P in shared memory only with tiles of 64 keys");
 #define AT_SMEM_BYTES (AT_Q_BYTES + AT_STAGES * 2 * AT_KV_BYTES + 2 * AT_P_BYTES + 1024 + 256)
-#define AT_TMEM_COLS 256                           // scores 2 x 64 columns, O from column 128
+#define AT_TMEM_COLS 256                           // scores 2 x 64 or 1 x 128 columns, O from column 128
 #define AT_O_COL 128
 #define AT_RESCALE_STEP 8.0f                       // log2 units a maximum may lag behind before O is rescaled
 
@@ -219,17 +228,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const uint32_t k_addr = tc_smem(kv_s + s * 2 * AT_KV_BYTES);
 #pragma unroll
         for (int kk = 0; kk < HEAD_DIM / 16; ++kk)
-          tc_mma(tmem_base + (i & 1) * AT_KT, tc_desc(q_addr + (kk >> 2) * (AT_ROWS * 128) + (kk & 3) * 32),
+          tc_mma(tmem_base + (i % AT_NBUF) * AT_KT, tc_desc(q_addr + (kk >> 2) * (AT_ROWS * 128) + (kk & 3) * 32),
                  tc_desc(k_addr + (kk >> 2) * AT_HALF_BYTES + (kk & 3) * 32), idesc_s, kk > 0 ? 1u : 0u);
-        tc_commit(&s_full[i & 1]);
+        tc_commit(&s_full[i % AT_NBUF]);
         return true;
       };
       bool ok = tc_wait(q_full, 0, abort_flag);
       if (ok) ok = issue_scores(0);
       for (int i = 0; i < ntiles && ok; ++i) {
-        if (i + 1 < ntiles) { ok = issue_scores(i + 1); if (!ok) break; }
+        // two score buffers: the next tile's scores are issued before this tile's P V; one buffer (P lies where the
+        // scores were): after it, and the tensor core runs them in the order of issue
+        if (AT_NBUF == 2 && i + 1 < ntiles) { ok = issue_scores(i + 1); if (!ok) break; }
         const int s = i % AT_STAGES;
-        if (!tc_wait(&p_full[i & 1], (i >> 1) & 1, abort_flag)) { ok = false; break; }
+        if (!tc_wait(&p_full[i % AT_NBUF], (i / AT_NBUF) & 1, abort_flag)) { ok = false; break; }
         if (!tc_wait(&v_full[s], (i / AT_STAGES) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t p_addr = tc_smem(p_s + (i & 1) * AT_P_BYTES);
@@ -237,14 +248,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
         for (int kk = 0; kk < AT_KT / 16; ++kk) {  // 16 keys: two groups of 8 rows of V
           if (AT_P_TMEM)                           // P: 8 columns of packed pairs per 16 keys, where the tile's scores were
-            at_mma_ts(tmem_base + AT_O_COL, tmem_base + (i & 1) * AT_KT + kk * 8, tc_desc_mn(v_addr + kk * 2048, AT_HALF_BYTES, 1024),
+            at_mma_ts(tmem_base + AT_O_COL, tmem_base + (i % AT_NBUF) * AT_KT + kk * 8, tc_desc_mn(v_addr + kk * 2048, AT_HALF_BYTES, 1024),
                       idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
           else                                     // P: 32 bytes along a row of the swizzled tile in shared memory
             tc_mma(tmem_base + AT_O_COL, tc_desc(p_addr + kk * 32), tc_desc_mn(v_addr + kk * 2048, AT_HALF_BYTES, 1024),
                    idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
         }
         tc_commit(&kv_empty[s]);
-        tc_commit(&pv_done[i & 1]);
+        tc_commit(&pv_done[i % AT_NBUF]);
+        if (AT_NBUF == 1 && i + 1 < ntiles) ok = issue_scores(i + 1);
       }
       pdl_launch_dependents();                      // all products of this block are issued
     }
@@ -264,28 +276,36 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       return __all_sync(0xffffffffu, tc_wait(bar, parity, abort_flag) ? 1 : 0) != 0;
     };
     for (int i = 0; i < ntiles; ++i) {
-      const int b = i & 1;
-      if (!wait_all(&s_full[b], (i >> 1) & 1)) { ok = false; break; }
+      const int b = i % AT_NBUF;
+      if (!wait_all(&s_full[b], (i / AT_NBUF) & 1)) { ok = false; break; }
       tc_fence_after();
-      uint32_t sv[AT_KT];
-      tc_ld32_issue(lane_addr + b * AT_KT, sv);
-      tc_ld32_issue(lane_addr + b * AT_KT + 32, sv + 32);
-      tc_ld_wait();
       const int key_base = (tile_begin + i) * AT_KT;
-      if (!(key_base + AT_KT - 1 <= pos && key_base >= lo)) {
+      const bool masked = !(key_base + AT_KT - 1 <= pos && key_base >= lo);
+      // 64 scores of this row: keys key_base + 64 * half ..; those the row may not see become -inf
+      uint32_t sv[64];
+      auto load64 = [&](int half) {
+        tc_ld32_issue(lane_addr + b * AT_KT + half * 64, sv);
+        tc_ld32_issue(lane_addr + b * AT_KT + half * 64 + 32, sv + 32);
+        tc_ld_wait();
+        if (masked) {
 #pragma unroll
-        for (int j = 0; j < AT_KT; ++j) {
-          const int key = key_base + j;
-          sv[j] = (key >= lo && key <= pos) ? sv[j] : 0xff800000u;       // -inf
+          for (int j = 0; j < 64; ++j) {
+            const int key = key_base + half * 64 + j;
+            sv[j] = (key >= lo && key <= pos) ? sv[j] : 0xff800000u;       // -inf
+          }
         }
-      }
-      // four independent chains of three-input maxima
+      };
+      // first pass: the row's maximum, four independent chains of three-input maxima
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 1
+      for (int half = 0; half < AT_KT / 64; ++half) {
+        load64(half);
 #pragma unroll
-      for (int j = 0; j < AT_KT; j += 8) {
+        for (int j = 0; j < 64; j += 8) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-          mx4[u] = at_max3(mx4[u], __uint_as_float(sv[j + 2 * u]), __uint_as_float(sv[j + 2 * u + 1]));
+          for (int u = 0; u < 4; ++u)
+            mx4[u] = at_max3(mx4[u], __uint_as_float(sv[j + 2 * u]), __uint_as_float(sv[j + 2 * u + 1]));
+        }
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // the maximum in use lags behind the true one by at most AT_RESCALE_STEP
@@ -294,21 +314,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const bool grow = cand > m_used + AT_RESCALE_STEP;          // also the first finite maximum
       if (grow) { factor = at_exp2(m_used - cand); m_used = cand; l *= factor; }
       const float sub = (m_used == -INFINITY) ? 0.f : m_used;
-      uint32_t pk[AT_KT / 2];
-      float sum8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      const float nsub = -sub;
-#pragma unroll
-      for (int j = 0; j < AT_KT; j += 2) {
-        float x0, x1;
-        at_fma2(x0, x1, __uint_as_float(sv[j]), __uint_as_float(sv[j + 1]), c, nsub);
-        const float p0 = at_exp2(x0), p1 = at_exp2(x1);
-        at_add2(sum8[j & 6], sum8[(j & 6) + 1], p0, p1);
-        pk[j >> 1] = at_pack(p0, p1);
-      }
-      l += ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
       // O rescale: the products of the tile before must have landed
       if (i > 0 && __any_sync(0xffffffffu, grow)) {
-        if (!wait_all(&pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1)) { ok = false; break; }
+        if (!wait_all(&pv_done[(i - 1) % AT_NBUF], ((i - 1) / AT_NBUF) & 1)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll 1
         for (int cc = 0; cc < HEAD_DIM; cc += 32) {
@@ -330,28 +338,48 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           const int half = e / (nzero * 8), rem = e - half * (nzero * 8);
           *reinterpret_cast<uint4*>(vst + half * AT_HALF_BYTES + (nvalid + (rem >> 3)) * 128 + ((rem & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
-      }
-      if (AT_P_TMEM) {
-        // P over the scores it came from (this thread has them in registers; the next scores for this buffer are
-        // issued after the product that reads P)
-        tc_st32(lane_addr + b * AT_KT, pk);
-        tc_st_wait();
-      } else {
-        // the P buffer is free once the products of tile i - 2 have read it
-        if (i >= 2 && !wait_all(&pv_done[b], ((i - 2) >> 1) & 1)) { ok = false; break; }
-        unsigned char* prow = p_s + b * AT_P_BYTES + r * 128;
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          uint4 v4 = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
-          *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = v4;
-        }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> the tensor core's reads
       }
+      // second pass: P = exp2(score * c - max in use), 64 keys at a time (tiles of 128 keys: read again from tensor
+      // memory, so that a row's scores never need 128 registers)
+      float sum8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      const float nsub = -sub;
+#pragma unroll 1
+      for (int half = 0; half < AT_KT / 64; ++half) {
+        if (AT_KT > 64) load64(half);
+        uint32_t pk[32];
+#pragma unroll
+        for (int j = 0; j < 64; j += 2) {
+          float x0, x1;
+          at_fma2(x0, x1, __uint_as_float(sv[j]), __uint_as_float(sv[j + 1]), c, nsub);
+          const float p0 = at_exp2(x0), p1 = at_exp2(x1);
+          at_add2(sum8[j & 6], sum8[(j & 6) + 1], p0, p1);
+          pk[j >> 1] = at_pack(p0, p1);
+        }
+        if (AT_P_TMEM) {
+          // P over the scores it came from: packed pairs, 32 columns per 64 keys.  With tiles of 128 keys the first
+          // half's P covers scores already read, and the second half's scores (columns 64..127) are still whole.
+          tc_st32(lane_addr + b * AT_KT + half * 32, pk);
+        } else {
+          // the P buffer is free once the products of tile i - 2 have read it
+          if (i >= 2 && !wait_all(&pv_done[b], ((i - 2) >> 1) & 1)) { ok = false; break; }
+          unsigned char* prow = p_s + b * AT_P_BYTES + r * 128;
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            uint4 v4 = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+            *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = v4;
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> the tensor core's reads
+        }
+      }
+      if (!ok) break;
+      l += ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
+      if (AT_P_TMEM) tc_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) tc_mbar_arrive(&p_full[b]);
     }
-    if (ok && ntiles > 0 && wait_all(&pv_done[(ntiles - 1) & 1], ((ntiles - 1) >> 1) & 1)) {
+    if (ok && ntiles > 0 && wait_all(&pv_done[(ntiles - 1) % AT_NBUF], ((ntiles - 1) / AT_NBUF) & 1)) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const int tk = valid ? row / G : 0, h = valid ? row - tk * G : 0;

@@ -792,6 +792,25 @@ def test_attention_tcgen05_portions(n_q, n_kv, d, ps, window):
     _tc_attention_case(n_q, n_kv, d, ps, window, lens, steps)
 
 
+@pytest.mark.parametrize("n_q,n_kv,ps,window", [(32, 8, 16, None), (6, 3, 32, 70), (7, 1, 8, 33), (16, 2, 64, None)])
+def test_attention_tcgen05_tiles_of_128_keys(n_q, n_kv, ps, window, monkeypatch):
+    """The build with key tiles of 128 (``-DAT_KT=128``, heads of 64: one score buffer in tensor memory, the row's
+    scores read twice): kept as an option because it was measured slower, and kept right."""
+    from photon_infer_b200.kernels import ops
+    real = ops.load_module
+
+    def wide_tiles(module, defines=None):
+        if module == "attention_tc" and defines and defines.get("HEAD_DIM") == 64:
+            defines = dict(defines, AT_KT=128)
+        return real(module, defines)
+    monkeypatch.setattr(ops, "load_module", wide_tiles)
+    lens = [200, 333, 700, 1, 90, 1100]
+    steps = [(0, 200), (150, 183), (699, 1), (0, 1), (60, 30), (513, 587)]
+    _tc_attention_case(n_q, n_kv, 64, ps, window, lens, steps)
+    for spike in (0, 63, 64, 127, 128, 600):
+        _tc_attention_case(4, 1, 64, 16, None, [700], [(640, 60)], seed=40 + spike, spike=spike)
+
+
 def test_attention_tcgen05_far_key_and_page_edges():
     """A key with a dominant score at a page edge, a tile edge and the far start; every row must land on
     its value row."""
