@@ -294,3 +294,42 @@ def test_captured_decode_steps_keep_their_scratch(tmp_path, monkeypatch):
     assert seen and runner.graph_kernel_launches > 0
     owned = {t.data_ptr() for t in ops._decode_scratch[("cuda", 0)]}
     assert all(t.data_ptr() in owned for t in seen)
+
+
+@pytest.mark.parametrize("name,dtype", [("tiny_a", "float32"), ("tiny_d", "bfloat16")])
+def test_graphs_that_come_and_go_change_no_token(folders, name, dtype):
+    """Requests that arrive and finish at different times run decode steps of many batch sizes and block-table
+    widths; with room for three captured graphs only, graphs are dropped and captured again all the time.  The
+    tokens must be those of an engine without graphs (float32: exactly; bfloat16: both are checked against the
+    plain implementation under the tie rule, because a graph pads its batch and padding changes no row)."""
+    from photon_infer_b200 import ContinuousBatchEngine
+    vocab = TINY[name]["config"]["vocab_size"]
+    prompts = [random_ids(5 + 11 * i, vocab, seed=300 + i) for i in range(7)]
+    lengths = [40, 9, 33, 21, 50, 14, 27]
+
+    def run(graphs):
+        eng = ContinuousBatchEngine(folders[name], _options(name, dtype, use_cuda_graphs=graphs, max_cache_tokens=4096))
+        if graphs:
+            eng.runner.max_graphs = 3
+        ids = []
+        pending = list(zip(prompts, lengths))
+        steps = 0
+        while pending or eng.has_work():
+            if pending and steps % 3 == 0:                   # one arrival every third step
+                p, n = pending.pop(0)
+                ids.append(eng.add_request(p, max_new_tokens=n, ignore_eos=True))
+            eng.step()
+            steps += 1
+        out = [list(eng.result(i).generated_tokens) for i in ids]
+        eng.runner.check_device_errors()
+        assert eng.runner.cache.free_pages() == [g.num_pages for g in eng.runner.cache.groups]
+        return out, eng
+    with_graphs, eng = run(True)
+    assert eng.runner.graph_kernel_launches > 0 and len(eng.runner._graphs) <= 3
+    without, _ = run(False)
+    assert [len(t) for t in with_graphs] == lengths
+    if dtype == "float32":
+        assert with_graphs == without
+    else:
+        for p, got in zip(prompts, with_graphs):
+            _plain_greedy_checked(folders[name], p, got, dtype)
