@@ -47,6 +47,9 @@ static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "head size of the TMA decode at
 #define AD_KD (HEAD_DIM / 16)
 #define AD_ND (HEAD_DIM / 8)
 #define AD_MAX_SEQS 512
+#ifndef AD_ADAPTIVE
+#define AD_ADAPTIVE 1                              // 0: the host's chunk size is used as it is (for comparisons)
+#endif
 #define AD_MAX_CHUNKS (HEAD_DIM < 120 ? HEAD_DIM : 120)   // chunks of one request: 16 rows x (chunks + 1) weights fit the merge buffer of 16 x (HEAD_DIM + 2) floats; a lane holds four
 #define AD_Q_BYTES (16 * HEAD_DIM * 2)              // the 16 query rows
 #define AD_MERGE_BYTES (16 * (HEAD_DIM + 2) * 4)    // one warp's partial result
@@ -204,7 +207,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 
   int* scan = reinterpret_cast<int*>(merge);                    // [AD_THREADS], before the first item only
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int G = P.group, CH = P.chunk_tiles;
+  const int G = P.group;
+  int CH = P.chunk_tiles;
   if (threadIdx.x == 0) {
     const int np = AD_TILE / P.box_rows < 4 ? AD_TILE / P.box_rows : 4;   // producer warps with work
     for (int s = 0; s < AD_STAGES; ++s) { tc_mbar_init(&full_bar[s], np); tc_mbar_init(&empty_bar[s], 4); }
@@ -232,6 +236,54 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   {
     const int span = (P.S + AD_THREADS - 1) / AD_THREADS;
     const int s_lo = threadIdx.x * span, s_hi = min(P.S, s_lo + span);
+    // The host chose chunk_tiles for requests as long as the block table allows (a captured step is replayed while
+    // its requests grow).  What the requests hold NOW decides better: the same rule as ops.attention_decode_plan,
+    // on the longest request of this step, within the room the host reserved for partial results.
+    if (AD_ADAPTIVE) {
+      int longest = 0, count = 0, total = 0;
+      for (int seq = s_lo; seq < s_hi; ++seq) {
+        int tok0, ntok, ctx, tb, te;
+        if (key_range(seq, tok0, ntok, ctx, tb, te)) { longest = max(longest, te - tb); ++count; total += te - tb; }
+      }
+      // over the block: shuffles inside a warp, then eight numbers through shared memory
+#pragma unroll
+      for (int o2 = 16; o2 > 0; o2 >>= 1) {
+        longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, o2));
+        count += __shfl_xor_sync(0xffffffffu, count, o2);
+        total += __shfl_xor_sync(0xffffffffu, total, o2);
+      }
+      if (lane == 0) { scan[warp] = longest; scan[8 + warp] = count; scan[24 + warp] = total; }
+      __syncthreads();
+      int tiles = 0, few = 0, sum = 0;
+#pragma unroll
+      for (int w = 0; w < AD_THREADS / 32; ++w) { tiles = max(tiles, scan[w]); few += scan[8 + w]; sum += scan[24 + w]; }
+      // The rule takes every request for as long as the longest: it is applied where that is nearly so (the mean at
+      // least 0.8 of the longest).  Requests of mixed lengths fill one another's gaps, and the host's cut was measured
+      // as good or better there (56 requests of 128 to 2,300 keys: 70 us with chunks of 22 tiles, 71 us whole).
+      // Thread t tries p = fewest chunks + t chunks per request; the cheapest wins, the longer chunk on a tie.
+      int key = 0x7fffffff;
+      if (tiles > 0 && few > 0 && (long)sum * 5 >= (long)tiles * few * 4) {
+        const long cap = P.scratch_chunks / few;                       // chunks a request may have
+        const int p_hi = (int)min((long)min(AD_MAX_CHUNKS, tiles), cap);
+        const int p = (tiles + 63) / 64 + (int)threadIdx.x;
+        if (p <= p_hi) {
+          const int chunk = (tiles + p - 1) / p;
+          if ((tiles + chunk - 1) / chunk == p) {
+            const long rounds = ((long)few * P.n_kv * p + gridDim.x - 1) / gridDim.x;
+            const long cost = rounds * (chunk + 5) * 10 + (p > 1 ? 3 * p : 0);
+            if (cost < (1L << 23)) key = (int)((cost << 7) | (64 - chunk));
+          }
+        }
+      }
+#pragma unroll
+      for (int o2 = 16; o2 > 0; o2 >>= 1) key = min(key, __shfl_xor_sync(0xffffffffu, key, o2));
+      if (lane == 0) scan[16 + warp] = key;
+      __syncthreads();
+#pragma unroll
+      for (int w = 0; w < AD_THREADS / 32; ++w) key = min(key, scan[16 + w]);
+      if (key != 0x7fffffff) CH = 64 - (key & 127);
+      __syncthreads();                                           // scan is used again below
+    }
     int mine = 0;
     for (int seq = s_lo; seq < s_hi; ++seq) {
       int tok0, ntok, ctx, tb, te;
@@ -697,7 +749,6 @@ PHOTON_API int photon_attention_decode(const void* q, long q_stride, void* out, 
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
-  long grid = slots;
-  if (max_items > 0 && max_items < grid) grid = max_items;
+  const long grid = slots;                          // blocks without an item leave at once; the kernel may cut finer than the host
   return launch_pdl(attention_decode_kernel, dim3((unsigned)grid), dim3(AD_THREADS), (size_t)AD_SMEM_BYTES, stream, map_q, map_k, map_v, P);
 }
