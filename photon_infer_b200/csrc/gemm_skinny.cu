@@ -240,14 +240,16 @@ static int skinny_launch(const void* x, long ldx, const void* W, long ldw, void*
   const int sms = photon_sm_count();
   const bool small_grid = row_blocks <= 4 * sms;
   const int unroll = ((rt * mt_pad <= 2) ? 4 : (rt * mt_pad <= 4 ? 2 : 1)) * ((small_grid && rt * mt_pad <= 1) ? 2 : 1);
-  // split K over blocks only where a warp would need more than two rounds of loads and the grid is
-  // small: the hand-over through global memory costs about as much as one round
-  // one block per SM or fewer and a long K: sixteen warps per block share K
-  const bool wide = mt <= 1 && small_grid && EPI != EPI_SWIGLU && row_blocks <= sms && K >= 4096;
+  // split K over blocks only where a warp would need more than two rounds of loads and the row tiles alone leave
+  // SMs without a block: the hand-over through global memory costs about as much as one round, and with a block
+  // on every SM it only adds to it (measured at 8 rows: 4,096 x 14,336 in 22.9 us unsplit against 32.2 us in
+  // halves, 3,072 x 8,192 in 13.3 against 16.8 us)
+  // one block per SM or fewer: sixteen warps per block share K (2,048 x 2,048: 4.7 us against 5.1 us with eight)
+  const bool wide = mt <= 1 && small_grid && EPI != EPI_SWIGLU && row_blocks <= sms && K >= 2048;
   const int warps = wide ? 16 : SK_WARPS;
   const int per_warp = ((K + 31) / 32 + warps - 1) / warps;
   int ks = 1;
-  while (ks < 8 && per_warp > 2 * unroll * ks && row_blocks * ks < 4 * sms) ks *= 2;
+  while (ks < 8 && per_warp > 2 * unroll * ks && row_blocks * ks < sms) ks *= 2;
   if (scratch == nullptr || tickets == nullptr || row_blocks > num_tickets) ks = 1;
   while (ks > 1 && (long)row_blocks * ks * rt * mt_pad * 128 > scratch_floats) ks /= 2;
   dim3 grid(ks, row_blocks);
