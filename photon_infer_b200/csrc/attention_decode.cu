@@ -1,19 +1,23 @@
 // Paged attention of decoded tokens for large batches and long contexts, bfloat16, head size 64 or 128.
 //
 // The requests of a step that bring at most 16 query rows (row = token_in_step * GROUP + head_in_group, the
-// packing of attention_flash.cu) have their keys cut into chunks of `chunk_tiles` tiles of 64 keys.  A work
-// item is (request, key/value head, chunk).  The grid is persistent: as many blocks as the GPU holds at
-// once, each taking items round-robin, so a step whose (request, head) pairs slightly outnumber the places
-// does not pay for a second, nearly empty wave, and requests of very different lengths weigh what they weigh.
-// The item list follows from the requests' lengths inside the kernel (a prefix sum over the requests), so a
-// captured graph serves every step of its shape.
+// packing of attention_flash.cu) have their keys cut into chunks of tiles of 64 keys.  A work item is
+// (request, key/value head, chunk).  The grid is persistent: as many blocks as the GPU holds at once, each
+// drawing items from a counter, so a step whose (request, head) pairs slightly outnumber the places does not
+// pay for a second, nearly empty wave, and requests of very different lengths weigh what they weigh.  The item
+// list follows from the requests' lengths inside the kernel (a prefix sum over the requests), so a captured
+// graph serves every step of its shape; the host gives a chunk length for the longest context the block table
+// allows, and the kernel shortens or lengthens it by the same rule for what requests of nearly one length
+// hold now.
 //
 // Keys and values come by TMA: one 2-D box per page part (16 keys x 64 features with pages of 16), 128-byte
-// swizzle, into a ring of stages, completion on an mbarrier.  One thread issues a whole tile (eight or sixteen
-// instructions); the 2,048 cp.async instructions with their address arithmetic that a tile costs in
-// attention_flash.cu made that kernel issue-bound (47 % of all issue slots at 18 % occupancy).  The four warps
-// of a block take 16 keys of every tile each: scores and weighted sums as mma.m16n8k16 with fragments read by
-// ldmatrix from the swizzled tiles, running softmax in 32-bit, merged in warp order through shared memory.
+// swizzle, into a ring of stages, completion on an mbarrier.  Four producer warps (they give their registers
+// to the others with setmaxnreg) issue a page part each, because a TMA instruction costs its thread 150 to 200
+// cycles and a tile is eight or sixteen of them; one of them draws the items and hands them to the consumers
+// through a small queue.  (The 2,048 cp.async instructions with their address arithmetic that a tile costs in
+// attention_flash.cu made that kernel issue-bound: 47 % of all issue slots at 18 % occupancy.)  The four
+// consumer warps take 16 keys of every tile each: scores and weighted sums as mma.m16n8k16 with fragments read
+// by ldmatrix from the swizzled tiles, running softmax in 32-bit, merged in warp order through shared memory.
 // A request with one chunk is written out directly; otherwise the item leaves (max, sum, weighted sum) in a
 // scratch buffer and the block that draws the last ticket of (request, head) merges the chunks in chunk order.
 //
