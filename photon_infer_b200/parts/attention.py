@@ -169,6 +169,10 @@ class PagedAttention(Mixer):
                 if self._max_groups is None:
                     self._max_groups = ops.flash_attention_max_groups(self.head_dim)
                 splits, groups = choose_key_shares(sum(few) * self.n_kv, keys, self._max_groups, sms=ops.sm_count(q.device))
+                # the kernel indexes its partial results by the token's place in the step, so beside a long prompt
+                # portion every share costs T rows: no more shares than 64 MB of them
+                per_share = T * self.n_q * (self.head_dim + 2) * 4
+                splits = max(1, min(splits, (64 << 20) // per_share))
                 if splits > 1:
                     scratch = torch.empty(T * self.n_q * splits * (self.head_dim + 2), dtype=torch.float32, device=q.device)
             if rows_mode and ops.USE_ATTENTION_TC and \
