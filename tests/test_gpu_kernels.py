@@ -578,6 +578,16 @@ def test_decode_attention_tma_far_key_and_more_requests_than_blocks():
     _decode_attention_case(8, 4, 64, 16, None, lens, [1] * len(lens), 1)
 
 
+@pytest.mark.parametrize("n_q,n_kv,d", [(32, 8, 64), (24, 8, 128)])
+def test_decode_attention_tma_cuts_requests_of_one_length_itself(n_q, n_kv, d):
+    """Requests of nearly one length with a chunk length from the host that suits them badly (one tile, or more
+    tiles than they have): the kernel chooses its own within the room it was given, and the result is the same."""
+    lens = [3000, 2900, 3100, 2950]
+    for chunk in (1, 2, 64):
+        _decode_attention_case(n_q, n_kv, d, 16, None, lens, [1] * len(lens), chunk)
+    _decode_attention_case(n_q, n_kv, d, 16, None, [700] * 40, [1] * 40, 1)
+
+
 def test_decode_attention_tma_refuses_what_it_cannot_take():
     from photon_infer_b200.errors import PhotonError
     from photon_infer_b200.kernels import ops
